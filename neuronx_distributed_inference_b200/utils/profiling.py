@@ -40,7 +40,7 @@ def ncu_launch_list_cmd(cmd: List[str], out_csv: str = "gpurun_out/launches.csv"
 
 
 def ncu_full_cmd(cmd: List[str], kernel_regex: str, out: str = "gpurun_out/prof", skip: int = 0, count: int = 3) -> str:
-    return " ".join(["ncu", "--set", "full", "--clock-control", "none", "--import-source", "on", "-k", f"regex:{kernel_regex}",
+    return " ".join(["ncu", "--set", "full", "--clock-control", "none", "-k", f"regex:{kernel_regex}",
                      "-s", str(skip), "-c", str(count), "-o", out, "-f"] + [shlex.quote(c) for c in cmd])
 
 

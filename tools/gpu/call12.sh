@@ -10,5 +10,5 @@ timeout 300 python bench.py --steps 64 --warmup 8 --skip-ci > gpurun_out/c12/ben
 timeout 300 python bench.py --steps 64 --warmup 8 --shard-shapes 8 > gpurun_out/c12/bench_tp8s_mega.json 2> gpurun_out/c12/bench_tp8s_mega.err
 NXDI_B200_DECODE_STEP=0 timeout 200 python tools/prof_decode.py --layers 4 --shard-shapes 8 > gpurun_out/c12/prof_tp8shapes_kern.txt 2>&1
 timeout 200 python tools/prof_decode.py --layers 4 --shard-shapes 8 > gpurun_out/c12/prof_tp8shapes_mega.txt 2>&1
-timeout 300 ncu --set full --clock-control none --import-source on -k regex:attention_kernel -s 2 -c 2 -o gpurun_out/c12/ncu_attn python tools/ncu_target.py > gpurun_out/c12/ncu_attn.log 2>&1
+timeout 300 ncu --set full --clock-control none -k regex:attention_kernel -s 2 -c 2 -o gpurun_out/c12/ncu_attn python tools/ncu_target.py > gpurun_out/c12/ncu_attn.log 2>&1
 for f in gpurun_out/c12/bench_*.json; do echo -n "$f "; python -c "import json,sys; d=json.load(open('$f')); print(round(d['ms_per_step'],3))"; done

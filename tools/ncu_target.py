@@ -1,6 +1,6 @@
 """Small launch list for ncu: the decode GEMVs of Llama-3.1-8B (TP1 shapes), the fused rope+attention decode kernel and one
 prefill GEMM, each preceded by warm-up launches.  Usage (one GPU):
-  ncu --set full --clock-control none --import-source on -k regex:gemv2_kernel -s 6 -c 2 -o gpurun_out/ncu_gemv2 python tools/ncu_target.py"""
+  ncu --set full --clock-control none -k regex:gemv2_kernel -s 6 -c 2 -o gpurun_out/ncu_gemv2 python tools/ncu_target.py"""
 import sys
 import torch
 sys.path.insert(0, ".")

@@ -1,6 +1,6 @@
 """ncu target: ONE launch of every hot kernel at a representative Llama-3.1-8B / DBRX shape inside a cudaProfiler range.
 
-  ncu --set full --clock-control none --import-source on --profile-from-start off -o gpurun_out/ncu_r2_all python tools/ncu_target_all.py
+  ncu --set full --clock-control none --profile-from-start off -o gpurun_out/ncu_r2_all python tools/ncu_target_all.py
 
 Warm-ups run outside the range (not profiled).  One GPU only.
 """

@@ -1,5 +1,5 @@
 """ncu launch list: the four decode GEMVs of one Llama-3.1-8B layer at TP=8 rank shapes (T=2), 4 rounds.
-  ncu --set full --clock-control none --import-source on -k regex:gemv2_kernel -s 12 -c 4 -o gpurun_out/ncu_gemv2_tp8 python tools/ncu_target_tp8.py"""
+  ncu --set full --clock-control none -k regex:gemv2_kernel -s 12 -c 4 -o gpurun_out/ncu_gemv2_tp8 python tools/ncu_target_tp8.py"""
 import sys
 import torch
 sys.path.insert(0, ".")
