@@ -65,6 +65,45 @@ class DecoderLayer(nn.Module):
         return h
 
 
+class PostNormDecoderLayer(nn.Module):
+    """Block whose norms come AFTER the sums: ``x <- norm1(alpha * x + mixer(x))``, then ``x <- norm2(alpha * x + mlp(x))`` when
+    the block has an MLP.  The sublayers read ``x`` itself; the residual stream and both norms are fp32 (one kernel per sum + norm),
+    and each norm also emits the stream in the activation dtype for the next projection (``meta.extras['lp_stream']``).
+    ``norm*`` are :class:`RMSNorm` modules (weight, eps, offset); ``mixer(x, meta, kv_mgr)`` is any sequence mixer."""
+    mlp_is_moe = False
+
+    def __init__(self, mixer: nn.Module, mlp: Optional[nn.Module], norm1: nn.Module, norm2: Optional[nn.Module], alpha: float,
+                 layer_idx: int = 0):
+        super().__init__()
+        self.mixer, self.mlp, self.norm1, self.norm2 = mixer, mlp, norm1, norm2
+        self.alpha, self.layer_idx = float(alpha), layer_idx
+
+    def state_specs(self):
+        return getattr(self.mixer, "state_specs", dict)()
+
+    @staticmethod
+    def low_precision(h, meta, dtype):
+        """The stream in the activation dtype: the copy the last norm wrote, or a cast."""
+        if dtype == torch.float32:
+            return h
+        src, lp = meta.extras.get("lp_stream", (None, None))
+        return lp if src is h and lp is not None else h.to(dtype)
+
+    def _sum_norm(self, h, y, norm, meta, dtype):
+        out, lp = ops.scaled_add_rmsnorm(h, y, norm.weight, self.alpha, norm.variance_epsilon, norm.offset, dtype)
+        meta.extras["lp_stream"] = (out, lp)
+        return out
+
+    def forward(self, h, meta, kv_mgr, lora=None):
+        dtype = meta.extras["act_dtype"]
+        h = self._sum_norm(h, self.mixer(self.low_precision(h, meta, dtype), meta, kv_mgr), self.norm1, meta, dtype)
+        if self.mlp is not None:
+            h = self._sum_norm(h, self.mlp(self.low_precision(h, meta, dtype)), self.norm2, meta, dtype)
+        if meta.capture is not None:
+            meta.capture[f"layers.{self.layer_idx}.out"] = h
+        return h
+
+
 class NeuronBaseModel(nn.Module):
     """Generic causal decoder.  Subclass hooks: ``setup_attr_for_model(config)`` (set
     ``tp_degree, hidden_size, num_attention_heads, num_key_value_heads, max_batch_size,
@@ -312,7 +351,11 @@ class NeuronBaseModel(nn.Module):
         if sp:
             h = mappings.all_gather(h.contiguous(), 1, self.tp_group)
         # ---- last-token gather (prefill) ------------------------------------------------------
-        if is_prefill and not all_positions:
+        gp = kw.get("gather_positions")
+        if gp is not None:
+            # explicit per-row token indices [B, K] whose logits are wanted (ragged batches: several per row, or none that matter)
+            h_out = torch.gather(h, 1, gp.long().clamp(0, h.shape[1] - 1).unsqueeze(-1).expand(-1, -1, h.shape[-1]))
+        elif is_prefill and not all_positions:
             if meta.key_valid is not None and self.padding_side == "right":
                 last = meta.key_valid.sum(-1).clamp_min(1) - 1
             elif self.padding_side == "right" and attention_mask is None:

@@ -31,6 +31,10 @@ class RecurrentStateCache(nn.Module):
         lines = lines.long()
         return torch.where((lines < 0) | (lines > self.num_lines), torch.full_like(lines, self.num_lines), lines)
 
+    def tensor(self, name: str) -> torch.Tensor:
+        """The whole ``[lines + 1, ...]`` buffer of a state (kernels index it by line themselves)."""
+        return getattr(self, self._names[name])
+
     def read(self, name: str, lines: torch.Tensor) -> torch.Tensor:
         return getattr(self, self._names[name])[self._lines(lines)]
 

@@ -68,3 +68,21 @@ class PlainMLP(nn.Module):
 
     def forward(self, x, residual=None):
         return self.fc2(ops.activation(self.fc1(x), self.act), residual)
+
+
+class ClampedGLUMLP(nn.Module):
+    """Gated MLP with a clamped, shifted gate product: ``g = min(W_gate x, limit)``, ``u = clamp(W_up x, -limit, limit)``,
+    ``y = W_down(g * sigmoid(alpha * g) * (u + 1))``.  The weights are stored ``[gate; up]`` like :class:`GatedMLP`; ``alpha`` and
+    ``limit`` are parameters of the layer (GPT-OSS experts use the same product with alpha 1.702, limit 7)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702, dtype=torch.float32,
+                 tp_group: Optional[Group] = None, device=None):
+        super().__init__()
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.gate_up_proj = ColumnParallelLinear(hidden_size, 2 * intermediate_size, bias=False, gather_output=False, dtype=dtype,
+                                                 device=device, tensor_model_parallel_group=tp_group, stride=2)
+        self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=False, input_is_parallel=True, dtype=dtype,
+                                           device=device, tensor_model_parallel_group=tp_group)
+
+    def forward(self, x):
+        return self.down_proj(ops.clamped_glu(self.gate_up_proj(x), self.limit, self.alpha))

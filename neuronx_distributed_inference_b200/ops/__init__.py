@@ -423,3 +423,84 @@ attention_with_mask = ref.attention_with_mask
 quantize_per_channel = ref.quantize_per_channel
 quantize_per_tensor = ref.quantize_per_tensor
 quantize_blockwise = ref.quantize_blockwise
+
+
+# ---- sequence mixers on ragged rows (csrc/seqmix.cu; definitions and conventions in ops/reference.py) ---------------------------
+_MIX_DTYPES = (torch.bfloat16, torch.float32)
+
+
+def _mix_cuda(x) -> bool:
+    return _use_cuda(x) and x.dtype in _MIX_DTYPES
+
+
+def _i32(t):
+    return t.to(torch.int32).contiguous()
+
+
+def scaled_add_rmsnorm(x, y, weight, alpha: float, eps: float, offset: float = 0.0, lp_dtype=None):
+    if _use_cuda(x) and x.dtype == torch.float32 and (y is None or y.dtype in _MIX_DTYPES):
+        stats["scaled_add_rmsnorm"] += 1
+        W = x.shape[-1]
+        lp = lp_dtype if lp_dtype not in (None, torch.float32) else None
+        out, out_lp = _C().scaled_add_rmsnorm(x.reshape(-1, W).contiguous(), None if y is None else y.reshape(-1, W).contiguous(),
+                                              weight, float(alpha), float(eps), float(offset), lp == torch.bfloat16)
+        return out.view(x.shape), (out_lp.view(x.shape) if lp is not None else None)
+    return ref.scaled_add_rmsnorm(x, y, weight, alpha, eps, offset, lp_dtype)
+
+
+def short_conv(u, weight, bias, state, slots, ctx_len, q_len, silu: bool = False):
+    if _mix_cuda(u) and u.stride(-1) == 1:
+        stats["short_conv"] += 1
+        return _C().short_conv(u, weight, bias, state, _i32(slots), _i32(ctx_len), _i32(q_len), bool(silu))
+    return ref.short_conv(u, weight, bias, state, slots, ctx_len, q_len, silu)
+
+
+def short_conv_update(u, state, slots, ctx_len, q_len):
+    if _mix_cuda(u) and u.stride(-1) == 1:
+        stats["short_conv_update"] += 1
+        return _C().short_conv_update(u, state, _i32(slots), _i32(ctx_len), _i32(q_len))
+    return ref.short_conv_update(u, state, slots, ctx_len, q_len)
+
+
+def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w, k_norm_w, eps, n_q, n_kv, D, Dv, cos, sin,
+                            k_cache, v_cache, block_table, out_dtype=None):
+    if _mix_cuda(qkv) and qkv.stride(-1) == 1:
+        stats["conv_qknorm_rope_append"] += 1
+        return _C().conv_qknorm_rope_append(qkv, conv_w, state, _i32(slots), _i32(ctx_len), _i32(q_len), q_norm_w, k_norm_w, float(eps),
+                                            int(n_q), int(n_kv), int(D), int(Dv), cos.float().contiguous(), sin.float().contiguous(),
+                                            k_cache, v_cache, None if block_table is None else _i32(block_table))
+    return ref.conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w, k_norm_w, eps, n_q, n_kv, D, Dv, cos, sin,
+                                       k_cache, v_cache, block_table, out_dtype)
+
+
+def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate=None):
+    if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1):
+        stats["paged_window_attention"] += 1
+        return _C().paged_window_attention(q.contiguous(), k_cache, v_cache, _i32(block_table), _i32(ctx_len), _i32(q_len), float(scale),
+                                           float(softcap or 0.0), int(window or 0), int(keep_first or 0), gate)
+    return ref.paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate)
+
+
+def ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads, head_dim, n_state, n_groups):
+    if _use_cuda(xBC) and xBC.dtype == torch.float32 and dt_raw.dtype in _MIX_DTYPES and state.dtype == torch.float32:
+        stats["ssd_scan"] += 1
+        return _C().ssd_scan(xBC.contiguous(), dt_raw, z, A_log, dt_bias, D_skip, state, _i32(slots), _i32(ctx_len), _i32(q_len),
+                             int(n_heads), int(head_dim), int(n_state), int(n_groups))
+    return ref.ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads, head_dim, n_state, n_groups)
+
+
+def group_rmsnorm(y, weight, groups: int, eps: float, out_dtype=None):
+    od = out_dtype or y.dtype
+    if _use_cuda(y) and y.dtype == torch.float32 and od in _MIX_DTYPES:
+        stats["group_rmsnorm"] += 1
+        W = y.shape[-1]
+        return _C().group_rmsnorm(y.reshape(-1, W).contiguous(), weight, int(groups), float(eps), od == torch.bfloat16).view(y.shape)
+    return ref.group_rmsnorm(y, weight, groups, eps, out_dtype)
+
+
+def clamped_glu(gu, limit: float, alpha: float = 1.702):
+    if _mix_cuda(gu):
+        stats["clamped_glu"] += 1
+        W = gu.shape[-1]
+        return _C().clamped_glu(gu.reshape(-1, W).contiguous(), float(limit), float(alpha)).view(*gu.shape[:-1], W // 2)
+    return ref.clamped_glu(gu, limit, alpha)

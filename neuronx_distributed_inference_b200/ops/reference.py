@@ -355,3 +355,165 @@ def rmsnorm_quant(x, weight, eps, clamp: float = float("inf")):
     amax = y.abs().amax(-1, keepdim=True).clamp_min(1e-12)
     scale = amax / 448.0
     return (y / scale).to(torch.float8_e4m3fn), scale
+
+
+# ---- sequence mixers on ragged rows -------------------------------------------------------------------------------------
+# Shared conventions of the ops below: activations are ``[B, T, ...]`` with row ``b`` holding ``q_len[b] <= T`` new tokens at
+# positions ``ctx_len[b] + t`` (the rest of the row is padding and is neither read nor written); per-sequence state lives in line
+# ``slots[b]`` of a state tensor and counts as zero for a row whose ``ctx_len`` is 0, so a slot that is handed to a new sequence
+# needs no clearing.
+
+def scaled_add_rmsnorm(x, y, weight, alpha: float, eps: float, offset: float = 0.0, lp_dtype=None):
+    """``out = rms_unit(alpha * x + y) * (offset + weight)`` in fp32 (``y`` may be None).  Returns ``(out fp32, out cast to lp_dtype
+    or None)`` — the second copy feeds the next projection."""
+    s = x.float() * alpha
+    if y is not None:
+        s = s + y.float()
+    out = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        out = out * (weight.float() + offset)
+    return out, (None if lp_dtype is None or lp_dtype == torch.float32 else out.to(lp_dtype))
+
+
+def _conv_window(u, state, slots, ctx_len):
+    """[B, K-1+T, C] fp32: each row's carried inputs (zeros for a fresh sequence) in front of its new ones."""
+    B = u.shape[0]
+    prev = state[slots.long()].float()
+    prev = torch.where((ctx_len > 0).view(B, 1, 1), prev, torch.zeros_like(prev))
+    return torch.cat([prev, u.float()], 1)
+
+
+def short_conv(u, weight, bias, state, slots, ctx_len, q_len, silu: bool = False):
+    """Causal depthwise convolution over time with carried inputs: ``y[b, t, c] = sum_j weight[c, j] * win[b, t + j, c]`` where
+    ``win`` is the row's last ``K - 1`` inputs followed by ``u``.  ``u`` [B, T, C], ``weight`` [C, K], ``state`` [lines, K-1, C].
+    Returns fp32; the state is NOT advanced (see :func:`short_conv_update`)."""
+    T, K = u.shape[1], weight.shape[1]
+    win = _conv_window(u, state, slots, ctx_len)
+    y = sum(win[:, j:j + T] * weight[:, j].float() for j in range(K))
+    if bias is not None:
+        y = y + bias.float()
+    return F.silu(y) if silu else y
+
+
+def short_conv_update(u, state, slots, ctx_len, q_len):
+    """Advance the carried inputs: line ``slots[b]`` becomes the last ``K - 1`` of (old inputs, ``u[b, :q_len[b]]``)."""
+    B, T, C = u.shape
+    Km1 = state.shape[1]
+    if Km1 == 0:
+        return
+    win = _conv_window(u, state, slots, ctx_len)
+    idx = (q_len.long().view(B, 1) + torch.arange(Km1, device=u.device).view(1, Km1)).unsqueeze(-1).expand(B, Km1, C)
+    new = win.gather(1, idx).to(state.dtype)
+    keep = (q_len > 0).view(B, 1, 1)
+    state[slots.long()] = torch.where(keep, new, state[slots.long()])
+
+
+def rope_partial_interleaved(x, cos, sin):
+    """x [B, T, H, D]; cos/sin [B, T, R/2]: channel pairs (2i, 2i+1), i < R/2, are rotated, the rest pass through."""
+    R = 2 * cos.shape[-1]
+    xr = x[..., :R].float().reshape(*x.shape[:-1], R // 2, 2)
+    c, s = cos.float().unsqueeze(2), sin.float().unsqueeze(2)
+    a, b = xr[..., 0], xr[..., 1]
+    rot = torch.stack([a * c - b * s, b * c + a * s], -1).reshape(*x.shape[:-1], R)
+    return torch.cat([rot, x[..., R:].float()], -1)
+
+
+def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w, k_norm_w, eps: float, n_q: int, n_kv: int,
+                            D: int, Dv: int, cos, sin, k_cache, v_cache, block_table, out_dtype=None):
+    """Fused front half of a convolved-projection attention layer.  ``qkv`` [B, T, >= n_q*D + n_kv*(D+Dv)] holds the biased q | k | v
+    projections (``n_kv = 0``: queries only, for a layer that reads another layer's cache).  Steps: short causal convolution of every
+    channel (carried inputs in ``state``), RMS norm of the WHOLE q row and of the WHOLE k row (plain weights), rotation of the first
+    ``2 * cos.shape[-1]`` channels of every q / k head, and the write of k (normed, rotated) and v (convolved only) into the paged
+    caches ``[blocks, page, n_kv, D | Dv]`` at position ``ctx_len + t``.  Returns q [B, T, n_q, D]."""
+    B, T = qkv.shape[:2]
+    Cq, Ck, Cv = n_q * D, n_kv * D, n_kv * Dv
+    C = Cq + Ck + Cv
+    y = short_conv(qkv[..., :C], conv_w, None, state, slots, ctx_len, q_len)
+    q = y[..., :Cq]
+    q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+    q = rope_partial_interleaved(q.view(B, T, n_q, D), cos, sin)
+    if n_kv:
+        k = y[..., Cq:Cq + Ck]
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+        k = rope_partial_interleaved(k.view(B, T, n_kv, D), cos, sin)
+        v = y[..., Cq + Ck:].view(B, T, n_kv, Dv)
+        page = k_cache.shape[1]
+        t = torch.arange(T, device=qkv.device).view(1, T)
+        pos = ctx_len.long().view(B, 1) + t
+        ok = t < q_len.long().view(B, 1)
+        blk = torch.gather(block_table.long(), 1, (pos // page).clamp(0, block_table.shape[1] - 1))
+        slot = (blk * page + pos % page)[ok]
+        k_cache.view(-1, n_kv, D)[slot] = k[ok].to(k_cache.dtype)
+        v_cache.view(-1, n_kv, Dv)[slot] = v[ok].to(v_cache.dtype)
+    return q.to(out_dtype or qkv.dtype)
+
+
+def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale: float, softcap: float, window: int,
+                           keep_first: int, gate=None):
+    """Soft-capped attention of ragged query rows over a paged cache that already holds their own keys.  Query at position
+    ``p = ctx_len + t`` sees key ``j`` iff ``j <= p and (p - j < window or j < keep_first)``; ``window <= 0`` means unbounded.
+    score = cap * tanh(scale * q.k / cap) (cap <= 0: none), softmax in fp32.  ``gate`` [B, T, Hq * Dv]: the output is multiplied by
+    ``sigmoid(gate)``.  q [B, T, Hq, D] -> [B, T, Hq * Dv]."""
+    B, T, Hq, D = q.shape
+    page, G, Dv = v_cache.shape[1], v_cache.shape[2], v_cache.shape[3]
+    bt = block_table.long().clamp_min(0)
+    k = k_cache[bt].reshape(B, -1, G, D).float()
+    v = v_cache[bt].reshape(B, -1, G, Dv).float()
+    S = k.shape[1]
+    p = (ctx_len.long().view(B, 1) + torch.arange(T, device=q.device).view(1, T)).unsqueeze(-1)          # [B, T, 1]
+    j = torch.arange(S, device=q.device).view(1, 1, S)
+    see = j <= p
+    if window and window > 0:
+        see = see & ((p - j < window) | (j < keep_first))
+    rep = Hq // G
+    s = torch.einsum("bthd,bshd->bhts", q.float(), k.repeat_interleave(rep, 2)) * scale
+    if softcap and softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    s = s.masked_fill(~see.unsqueeze(1), float("-inf"))
+    o = torch.einsum("bhts,bshd->bthd", torch.softmax(s, -1), v.repeat_interleave(rep, 2)).reshape(B, T, Hq * Dv)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    valid = (torch.arange(T, device=q.device).view(1, T) < q_len.long().view(B, 1)).unsqueeze(-1)
+    return torch.where(valid, o, torch.zeros_like(o)).to(q.dtype)
+
+
+def ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads: int, head_dim: int, n_state: int,
+             n_groups: int):
+    """Mamba-2 recurrence with a carried fp32 state ``[lines, n_heads, n_state, head_dim]``.  ``xBC`` [B, T, inner + 2 G N] is
+    x | B | C after convolution and SiLU; per head ``h`` (group ``h // (n_heads / G)``), with ``dt = softplus(dt_raw + dt_bias)``:
+    ``S <- exp(-exp(A_log) dt) S + dt B x^T``, ``y = S^T C + D_skip x``.  Returns ``y * silu(z)`` in fp32 [B, T, inner]; padding
+    steps leave the state untouched."""
+    B, T = xBC.shape[:2]
+    nh, P, N, G = n_heads, head_dim, n_state, n_groups
+    inner = nh * P
+    x = xBC[..., :inner].float().view(B, T, nh, P)
+    Bm = xBC[..., inner:inner + G * N].float().view(B, T, G, N).repeat_interleave(nh // G, 2)
+    Cm = xBC[..., inner + G * N:inner + 2 * G * N].float().view(B, T, G, N).repeat_interleave(nh // G, 2)
+    dt = F.softplus(dt_raw.float() + dt_bias.float(), threshold=1e9)
+    dA = torch.exp(-torch.exp(A_log.float()) * dt)
+    S = state[slots.long()].float()
+    S = torch.where((ctx_len > 0).view(B, 1, 1, 1), S, torch.zeros_like(S))
+    ys = []
+    for t in range(T):
+        live = (t < q_len).view(B, 1, 1, 1)
+        S_new = S * dA[:, t, :, None, None] + (dt[:, t, :, None] * Bm[:, t])[..., None] * x[:, t, :, None, :]
+        S = torch.where(live, S_new, S)
+        ys.append((S * Cm[:, t, :, :, None]).sum(2))
+    state[slots.long()] = torch.where((q_len > 0).view(B, 1, 1, 1), S, state[slots.long()].float()).to(state.dtype)
+    y = torch.stack(ys, 1) + x * D_skip.float().view(1, 1, nh, 1)
+    return y.reshape(B, T, inner) * F.silu(z.float())
+
+
+def group_rmsnorm(y, weight, groups: int, eps: float, out_dtype=None):
+    """RMS norm of ``groups`` equal parts of the last axis, each by its own root mean square, times ``weight``."""
+    yf = y.float().reshape(*y.shape[:-1], groups, y.shape[-1] // groups)
+    yf = (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + eps)).reshape(y.shape)
+    return (yf * weight.float()).to(out_dtype or y.dtype)
+
+
+def clamped_glu(gu, limit: float, alpha: float = 1.702):
+    """``[gate | up]`` halves -> ``g * sigmoid(alpha * g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``."""
+    g, u = gu.float().chunk(2, -1)
+    g = g.clamp(max=limit)
+    u = u.clamp(-limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)

@@ -97,7 +97,29 @@ MODEL_TYPES.update({"minicpm": {"causal-lm": f"{_B}:NeuronMiniCPMForCausalLM"}, 
                                      "audio-text-to-text": "neuronx_distributed_inference_b200.contrib.models.qwen2_5_omni:NeuronQwen2_5OmniThinkerForCausalLM"}})
 MODEL_TYPES.update({"wav2vec2": {"audio-frame-classification":
                                  "neuronx_distributed_inference_b200.contrib.models.wav2vec2:NeuronWav2Vec2ForAudioFrameClassification"}})
+MODEL_TYPES["fetodra"] = {"causal-lm": f"{_P}.fetodra.modeling_fetodra:NeuronFetodraForCausalLM"}
+# checkpoints that name their design by ``architecture`` instead of a Hugging Face ``model_type``
+ARCHITECTURES = {"Fetodra": "fetodra"}
 TASK_TYPES = ("causal-lm", "image-text-to-text", "speech-to-text", "text-to-image", "audio-frame-classification", "audio-text-to-text")
+
+
+def model_type_of(model_path: str) -> str:
+    """The registry key of the checkpoint in ``model_path`` from its config.json (``model_type``, else ``architecture`` /
+    ``architectures``)."""
+    import json
+    import os
+    with open(os.path.join(model_path, "config.json")) as f:
+        cfg = json.load(f)
+    mt = cfg.get("model_type")
+    if mt in MODEL_TYPES:
+        return mt
+    names = cfg.get("architectures") or []
+    if cfg.get("architecture"):
+        names = [cfg["architecture"]] + list(names)
+    for n in names:
+        if n in ARCHITECTURES:
+            return ARCHITECTURES[n]
+    raise ValueError(f"{model_path}/config.json names no model type this engine knows (model_type={mt!r}, architectures={names})")
 
 
 def get_model_cls(model_type: str, task_type: str = "causal-lm"):
