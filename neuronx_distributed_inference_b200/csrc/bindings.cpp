@@ -711,9 +711,11 @@ void dstep_launch_b(int64_t h, const at::Tensor& positions, const at::Tensor& wr
   dstep_launch(h, positions.data_ptr<int>(), write_pos.data_ptr<int>(), lines.data_ptr<int>(), cos.data_ptr<float>(),
                sin.data_ptr<float>(), (int)call_base, (int)parity_base, cur_stream());
 }
+void register_seqmix(pybind11::module_& m);   // seqmix_bind.cpp
 }  // namespace nxdi
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  nxdi::register_seqmix(m);
   m.def("symm_heap_create", [](int64_t bytes, int64_t dev, int64_t world, int64_t rank) { return (int64_t)nxdi::symm_heap_create(bytes, (int)dev, (int)world, (int)rank); });
   m.def("symm_heap_size", [](int64_t h) { return (int64_t)nxdi::symm_heap_size(h); });
   m.def("symm_heap_local_va", [](int64_t h) { return (int64_t)nxdi::symm_heap_local_va(h); });

@@ -1,0 +1,68 @@
+// Raw-pointer launchers of the ragged sequence-mixer kernels (seqmix.cu).  Conventions shared by all of them: activations are
+// [B, T, ...]; row b holds q_len[b] <= T live tokens at positions ctx_len[b] + t; per-sequence state sits in line lines[b] of a state
+// tensor and counts as zero when ctx_len[b] == 0.  `lp` selects the activation type: true = bf16, false = fp32.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nxdi {
+
+constexpr int SEQMIX_MAX_TAPS = 8;       // short convolutions: taps per channel
+constexpr int SEQMIX_MAX_VDIM = 256;     // attention: value channels per head
+constexpr int SEQMIX_MAX_STATE = 256;    // scan: state size per head
+
+void scaled_add_rmsnorm_launch(const float* x, const void* y, bool y_lp, const float* w, float* out, void* out_lp, int rows, int W,
+                               float alpha, float eps, float offset, cudaStream_t st);
+
+void short_conv_launch(const void* u, long long u_sb, long long u_st, const float* w, const float* bias, const void* state,
+                       const int* lines, const int* ctx_len, const int* q_len, float* y, int B, int T, int C, int K, bool silu, bool lp,
+                       cudaStream_t st);
+
+void short_conv_update_launch(const void* u, long long u_sb, long long u_st, void* state, const int* lines, const int* ctx_len,
+                              const int* q_len, int B, int T, int C, int K, bool lp, cudaStream_t st);
+
+struct ConvQkParams {
+  const void* p;            // [B, T, >= Cq + Ck + Cv] projections, row strides below
+  long long p_sb, p_st;
+  const float* conv_w;      // [Cq + Ck + Cv, K]
+  const void* state;        // [lines, K - 1, Cq + Ck + Cv]
+  const int *lines, *ctx_len, *q_len;
+  const float *q_norm_w, *k_norm_w;
+  const float *cos, *sin;   // [B, T, R / 2]
+  void* q_out;              // [B, T, n_q, D]
+  void *k_cache, *v_cache;  // [blocks, page, n_kv, D | Dv]
+  const int* block_table;   // [B, max_blocks]
+  int B, T, K, n_q, n_kv, D, Dv, R, page, max_blocks;
+  float eps;
+};
+void conv_qknorm_rope_append_launch(const ConvQkParams& p, bool lp, cudaStream_t st);
+
+struct WindowAttnParams {
+  const void* q;            // [B, T, Hq, D]
+  const void *k_cache, *v_cache;
+  const int *block_table, *ctx_len, *q_len;
+  const void* gate;         // [B, T, Hq * Dv] with row strides below, or null
+  long long g_sb, g_st;
+  void* out;                // [B, T, Hq * Dv]
+  int B, T, Hq, G, D, Dv, page, max_blocks, window, keep_first;
+  float scale, softcap;
+};
+void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStream_t st);
+
+struct SsdScanParams {
+  const float* xBC;         // [B, T, inner + 2 G N] after convolution and SiLU
+  const void *dt_raw, *z;   // strided views of the in-projection, activation type
+  long long dt_sb, dt_st, z_sb, z_st;
+  const float *A_log, *dt_bias, *D_skip;
+  float* state;             // [lines, nh, N, P]
+  const int *lines, *ctx_len, *q_len;
+  float* y;                 // [B, T, inner] = (S^T C + D x) * silu(z)
+  int B, T, nh, P, N, G;
+};
+void ssd_scan_launch(const SsdScanParams& p, bool lp, cudaStream_t st);
+
+void group_rmsnorm_launch(const float* y, const float* w, void* out, bool out_lp, int rows, int W, int groups, float eps, cudaStream_t st);
+
+void clamped_glu_launch(const void* gu, void* out, long long rows, int F, float limit, float alpha, bool lp, cudaStream_t st);
+
+}  // namespace nxdi

@@ -1,0 +1,240 @@
+// pybind11 surface of the ragged sequence-mixer kernels (seqmix.cu); registered into the extension module by bindings.cpp.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "seqmix.h"
+
+namespace nxdi {
+namespace {
+
+using OptT = c10::optional<at::Tensor>;
+inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream(); }
+inline bool is_f32(const at::Tensor& t) { return t.scalar_type() == at::kFloat; }
+inline bool is_lp(const at::Tensor& t) { return t.scalar_type() == at::kBFloat16; }
+inline void check_act(const at::Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda() && (is_f32(t) || is_lp(t)), what, ": CUDA tensor of bfloat16 or float32");
+}
+inline void check_f32(const at::Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda() && is_f32(t) && t.is_contiguous(), what, ": contiguous float32 CUDA tensor");
+}
+inline void check_i32(const at::Tensor& t, int64_t n, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous() && t.numel() >= n, what, ": contiguous int32 CUDA tensor");
+}
+// [B, T, C] view whose last axis is dense and whose rows are evenly strided
+inline void check_rows(const at::Tensor& t, const char* what) {
+  TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1, what, ": [B, T, C] with a dense last axis");
+}
+
+std::tuple<at::Tensor, at::Tensor> scaled_add_rmsnorm(const at::Tensor& x, const OptT& y, const OptT& w, double alpha, double eps,
+                                                      double offset, bool want_lp) {
+  check_f32(x, "scaled_add_rmsnorm x");
+  TORCH_CHECK(x.dim() == 2);
+  if (y.has_value()) {
+    check_act(*y, "scaled_add_rmsnorm y");
+    TORCH_CHECK(y->is_contiguous() && y->sizes() == x.sizes());
+  }
+  if (w.has_value()) {
+    check_f32(*w, "scaled_add_rmsnorm weight");
+    TORCH_CHECK(w->numel() == x.size(1));
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = at::empty_like(x);
+  at::Tensor lp = want_lp ? at::empty(x.sizes(), x.options().dtype(at::kBFloat16)) : at::Tensor();
+  scaled_add_rmsnorm_launch(x.data_ptr<float>(), y.has_value() ? y->data_ptr() : nullptr, y.has_value() && is_lp(*y),
+                            w.has_value() ? w->data_ptr<float>() : nullptr, out.data_ptr<float>(), want_lp ? lp.data_ptr() : nullptr,
+                            (int)x.size(0), (int)x.size(1), (float)alpha, (float)eps, (float)offset, stream());
+  return {out, want_lp ? lp : out};
+}
+
+void check_conv(const at::Tensor& u, const at::Tensor& w, const at::Tensor& state, const at::Tensor& lines, const at::Tensor& ctx,
+                const at::Tensor& qlen) {
+  check_act(u, "short_conv input");
+  check_rows(u, "short_conv input");
+  check_f32(w, "short_conv weight");
+  const int64_t B = u.size(0), C = u.size(2), K = w.size(1);
+  TORCH_CHECK(w.dim() == 2 && w.size(0) == C && K >= 1 && K <= SEQMIX_MAX_TAPS, "short_conv: weight [C, taps], taps <= ", SEQMIX_MAX_TAPS);
+  TORCH_CHECK(state.is_cuda() && state.scalar_type() == u.scalar_type() && state.is_contiguous() && state.dim() == 3 &&
+              state.size(1) == K - 1 && state.size(2) == C, "short_conv: state [lines, taps - 1, C] of the input's type");
+  check_i32(lines, B, "lines");
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+}
+
+at::Tensor short_conv(const at::Tensor& u, const at::Tensor& w, const OptT& bias, const at::Tensor& state, const at::Tensor& lines,
+                      const at::Tensor& ctx, const at::Tensor& qlen, bool silu) {
+  check_conv(u, w, state, lines, ctx, qlen);
+  if (bias.has_value()) check_f32(*bias, "short_conv bias");
+  c10::cuda::CUDAGuard guard(u.device());
+  auto y = at::zeros({u.size(0), u.size(1), u.size(2)}, u.options().dtype(at::kFloat));
+  short_conv_launch(u.data_ptr(), u.stride(0), u.stride(1), w.data_ptr<float>(), bias.has_value() ? bias->data_ptr<float>() : nullptr,
+                    state.data_ptr(), lines.data_ptr<int>(), ctx.data_ptr<int>(), qlen.data_ptr<int>(), y.data_ptr<float>(),
+                    (int)u.size(0), (int)u.size(1), (int)u.size(2), (int)w.size(1), silu, is_lp(u), stream());
+  return y;
+}
+
+void short_conv_update(const at::Tensor& u, at::Tensor state, const at::Tensor& lines, const at::Tensor& ctx, const at::Tensor& qlen) {
+  check_act(u, "short_conv_update input");
+  check_rows(u, "short_conv_update input");
+  const int64_t B = u.size(0), C = u.size(2), K = state.size(1) + 1;
+  TORCH_CHECK(state.is_cuda() && state.scalar_type() == u.scalar_type() && state.is_contiguous() && state.dim() == 3 && state.size(2) == C &&
+              K <= SEQMIX_MAX_TAPS);
+  check_i32(lines, B, "lines");
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+  c10::cuda::CUDAGuard guard(u.device());
+  short_conv_update_launch(u.data_ptr(), u.stride(0), u.stride(1), state.data_ptr(), lines.data_ptr<int>(), ctx.data_ptr<int>(),
+                           qlen.data_ptr<int>(), (int)B, (int)u.size(1), (int)C, (int)K, is_lp(u), stream());
+}
+
+at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w, const at::Tensor& state, const at::Tensor& lines,
+                                   const at::Tensor& ctx, const at::Tensor& qlen, const at::Tensor& q_norm_w, const OptT& k_norm_w, double eps,
+                                   int64_t n_q, int64_t n_kv, int64_t D, int64_t Dv, const at::Tensor& cos, const at::Tensor& sin,
+                                   at::Tensor k_cache, at::Tensor v_cache, const OptT& block_table) {
+  check_act(p, "conv_qknorm_rope_append projections");
+  check_rows(p, "conv_qknorm_rope_append projections");
+  const int64_t B = p.size(0), T = p.size(1), C = n_q * D + n_kv * (D + Dv), K = conv_w.size(1);
+  TORCH_CHECK(p.size(2) >= C && D % 2 == 0, "conv_qknorm_rope_append: projection narrower than q | k | v, or odd head size");
+  check_f32(conv_w, "conv weight");
+  TORCH_CHECK(conv_w.dim() == 2 && conv_w.size(0) == C && K >= 1 && K <= SEQMIX_MAX_TAPS);
+  TORCH_CHECK(state.is_cuda() && state.scalar_type() == p.scalar_type() && state.is_contiguous() && state.dim() == 3 &&
+              state.size(1) == K - 1 && state.size(2) == C, "conv_qknorm_rope_append: state [lines, taps - 1, q | k | v channels]");
+  check_i32(lines, B, "lines");
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+  check_f32(q_norm_w, "q norm weight");
+  TORCH_CHECK(q_norm_w.numel() == n_q * D);
+  check_f32(cos, "cos");
+  check_f32(sin, "sin");
+  TORCH_CHECK(cos.dim() == 3 && cos.size(0) == B && cos.size(1) == T && sin.sizes() == cos.sizes());
+  const int64_t R = 2 * cos.size(2);
+  TORCH_CHECK(R <= D, "rotated channels exceed the head size");
+  ConvQkParams a{};
+  if (n_kv > 0) {
+    TORCH_CHECK(k_norm_w.has_value() && block_table.has_value());
+    check_f32(*k_norm_w, "k norm weight");
+    TORCH_CHECK(k_norm_w->numel() == n_kv * D);
+    TORCH_CHECK(k_cache.is_cuda() && k_cache.scalar_type() == p.scalar_type() && k_cache.is_contiguous() && k_cache.dim() == 4 &&
+                k_cache.size(2) == n_kv && k_cache.size(3) == D, "k cache [blocks, page, kv heads, D] of the activation type");
+    TORCH_CHECK(v_cache.is_cuda() && v_cache.scalar_type() == p.scalar_type() && v_cache.is_contiguous() && v_cache.dim() == 4 &&
+                v_cache.size(0) == k_cache.size(0) && v_cache.size(1) == k_cache.size(1) && v_cache.size(2) == n_kv && v_cache.size(3) == Dv);
+    TORCH_CHECK(block_table->is_cuda() && block_table->scalar_type() == at::kInt && block_table->is_contiguous() && block_table->dim() == 2 &&
+                block_table->size(0) == B);
+    a.k_norm_w = k_norm_w->data_ptr<float>();
+    a.k_cache = k_cache.data_ptr();
+    a.v_cache = v_cache.data_ptr();
+    a.block_table = block_table->data_ptr<int>();
+    a.page = (int)k_cache.size(1);
+    a.max_blocks = (int)block_table->size(1);
+  }
+  c10::cuda::CUDAGuard guard(p.device());
+  auto q = at::zeros({B, T, n_q, D}, p.options());
+  a.p = p.data_ptr(); a.p_sb = p.stride(0); a.p_st = p.stride(1);
+  a.conv_w = conv_w.data_ptr<float>(); a.state = state.data_ptr();
+  a.lines = lines.data_ptr<int>(); a.ctx_len = ctx.data_ptr<int>(); a.q_len = qlen.data_ptr<int>();
+  a.q_norm_w = q_norm_w.data_ptr<float>();
+  a.cos = cos.data_ptr<float>(); a.sin = sin.data_ptr<float>();
+  a.q_out = q.data_ptr();
+  a.B = (int)B; a.T = (int)T; a.K = (int)K; a.n_q = (int)n_q; a.n_kv = (int)n_kv; a.D = (int)D; a.Dv = (int)Dv; a.R = (int)R;
+  a.eps = (float)eps;
+  conv_qknorm_rope_append_launch(a, is_lp(p), stream());
+  return q;
+}
+
+at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table,
+                                  const at::Tensor& ctx, const at::Tensor& qlen, double scale, double softcap, int64_t window,
+                                  int64_t keep_first, const OptT& gate) {
+  check_act(q, "paged_window_attention q");
+  TORCH_CHECK(q.dim() == 4 && q.is_contiguous());
+  const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), D = q.size(3);
+  TORCH_CHECK(k_cache.is_cuda() && k_cache.scalar_type() == q.scalar_type() && k_cache.is_contiguous() && k_cache.dim() == 4 && k_cache.size(3) == D);
+  TORCH_CHECK(v_cache.is_cuda() && v_cache.scalar_type() == q.scalar_type() && v_cache.is_contiguous() && v_cache.dim() == 4 &&
+              v_cache.size(0) == k_cache.size(0) && v_cache.size(1) == k_cache.size(1) && v_cache.size(2) == k_cache.size(2));
+  const int64_t G = k_cache.size(2), Dv = v_cache.size(3);
+  TORCH_CHECK(Hq % G == 0 && Dv <= SEQMIX_MAX_VDIM, "paged_window_attention: heads must divide, value size <= ", SEQMIX_MAX_VDIM);
+  TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == at::kInt && block_table.is_contiguous() && block_table.dim() == 2 &&
+              block_table.size(0) == B);
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+  WindowAttnParams a{};
+  if (gate.has_value()) {
+    check_rows(*gate, "gate");
+    TORCH_CHECK(gate->is_cuda() && gate->scalar_type() == q.scalar_type() && gate->size(0) == B && gate->size(1) == T && gate->size(2) == Hq * Dv);
+    a.gate = gate->data_ptr(); a.g_sb = gate->stride(0); a.g_st = gate->stride(1);
+  }
+  c10::cuda::CUDAGuard guard(q.device());
+  auto out = at::zeros({B, T, Hq * Dv}, q.options());
+  a.q = q.data_ptr(); a.k_cache = k_cache.data_ptr(); a.v_cache = v_cache.data_ptr();
+  a.block_table = block_table.data_ptr<int>(); a.ctx_len = ctx.data_ptr<int>(); a.q_len = qlen.data_ptr<int>();
+  a.out = out.data_ptr();
+  a.B = (int)B; a.T = (int)T; a.Hq = (int)Hq; a.G = (int)G; a.D = (int)D; a.Dv = (int)Dv; a.page = (int)k_cache.size(1);
+  a.max_blocks = (int)block_table.size(1); a.window = (int)window; a.keep_first = (int)keep_first;
+  a.scale = (float)scale; a.softcap = (float)softcap;
+  paged_window_attention_launch(a, is_lp(q), stream());
+  return out;
+}
+
+at::Tensor ssd_scan(const at::Tensor& xBC, const at::Tensor& dt_raw, const at::Tensor& z, const at::Tensor& A_log, const at::Tensor& dt_bias,
+                    const at::Tensor& D_skip, at::Tensor state, const at::Tensor& lines, const at::Tensor& ctx, const at::Tensor& qlen,
+                    int64_t nh, int64_t P, int64_t N, int64_t G) {
+  check_f32(xBC, "ssd_scan xBC");
+  const int64_t B = xBC.size(0), T = xBC.size(1), inner = nh * P;
+  TORCH_CHECK(xBC.dim() == 3 && xBC.size(2) == inner + 2 * G * N && nh % G == 0 && N <= SEQMIX_MAX_STATE, "ssd_scan: xBC [B, T, inner + 2 G N], N <= ",
+              SEQMIX_MAX_STATE);
+  check_act(dt_raw, "ssd_scan dt");
+  check_rows(dt_raw, "ssd_scan dt");
+  check_rows(z, "ssd_scan z");
+  TORCH_CHECK(z.is_cuda() && z.scalar_type() == dt_raw.scalar_type() && dt_raw.size(0) == B && dt_raw.size(1) == T && dt_raw.size(2) == nh &&
+              z.size(0) == B && z.size(1) == T && z.size(2) == inner);
+  check_f32(A_log, "A_log"); check_f32(dt_bias, "dt_bias"); check_f32(D_skip, "D");
+  TORCH_CHECK(A_log.numel() == nh && dt_bias.numel() == nh && D_skip.numel() == nh);
+  check_f32(state, "ssd_scan state");
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == nh && state.size(2) == N && state.size(3) == P, "ssd_scan: state [lines, heads, N, head_dim]");
+  check_i32(lines, B, "lines"); check_i32(ctx, B, "ctx_len"); check_i32(qlen, B, "q_len");
+  c10::cuda::CUDAGuard guard(xBC.device());
+  auto y = at::zeros({B, T, inner}, xBC.options());
+  SsdScanParams a{};
+  a.xBC = xBC.data_ptr<float>(); a.dt_raw = dt_raw.data_ptr(); a.z = z.data_ptr();
+  a.dt_sb = dt_raw.stride(0); a.dt_st = dt_raw.stride(1); a.z_sb = z.stride(0); a.z_st = z.stride(1);
+  a.A_log = A_log.data_ptr<float>(); a.dt_bias = dt_bias.data_ptr<float>(); a.D_skip = D_skip.data_ptr<float>();
+  a.state = state.data_ptr<float>(); a.lines = lines.data_ptr<int>(); a.ctx_len = ctx.data_ptr<int>(); a.q_len = qlen.data_ptr<int>();
+  a.y = y.data_ptr<float>();
+  a.B = (int)B; a.T = (int)T; a.nh = (int)nh; a.P = (int)P; a.N = (int)N; a.G = (int)G;
+  ssd_scan_launch(a, is_lp(dt_raw), stream());
+  return y;
+}
+
+at::Tensor group_rmsnorm(const at::Tensor& y, const at::Tensor& w, int64_t groups, double eps, bool out_lp) {
+  check_f32(y, "group_rmsnorm input");
+  check_f32(w, "group_rmsnorm weight");
+  TORCH_CHECK(y.dim() == 2 && groups >= 1 && y.size(1) % groups == 0 && w.numel() == y.size(1));
+  c10::cuda::CUDAGuard guard(y.device());
+  auto out = at::empty(y.sizes(), y.options().dtype(out_lp ? at::kBFloat16 : at::kFloat));
+  group_rmsnorm_launch(y.data_ptr<float>(), w.data_ptr<float>(), out.data_ptr(), out_lp, (int)y.size(0), (int)y.size(1), (int)groups, (float)eps,
+                       stream());
+  return out;
+}
+
+at::Tensor clamped_glu(const at::Tensor& gu, double limit, double alpha) {
+  check_act(gu, "clamped_glu input");
+  TORCH_CHECK(gu.dim() == 2 && gu.is_contiguous() && gu.size(1) % 2 == 0);
+  c10::cuda::CUDAGuard guard(gu.device());
+  auto out = at::empty({gu.size(0), gu.size(1) / 2}, gu.options());
+  clamped_glu_launch(gu.data_ptr(), out.data_ptr(), gu.size(0), (int)(gu.size(1) / 2), (float)limit, (float)alpha, is_lp(gu), stream());
+  return out;
+}
+
+}  // namespace
+
+void register_seqmix(pybind11::module_& m) {
+  m.def("scaled_add_rmsnorm", &scaled_add_rmsnorm);
+  m.def("short_conv", &short_conv);
+  m.def("short_conv_update", &short_conv_update);
+  m.def("conv_qknorm_rope_append", &conv_qknorm_rope_append);
+  m.def("paged_window_attention", &paged_window_attention);
+  m.def("ssd_scan", &ssd_scan);
+  m.def("group_rmsnorm", &group_rmsnorm);
+  m.def("clamped_glu", &clamped_glu);
+}
+
+}  // namespace nxdi

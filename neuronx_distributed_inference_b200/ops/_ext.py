@@ -24,6 +24,8 @@ _mod = None
 _tried = False
 
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
+# translation units whose results must match fp32 definitions closely: accurate tanh / exp / division instead of --use_fast_math
+PRECISE = {"seqmix.cu"}
 
 
 def sources():
@@ -61,7 +63,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     for src in sources():
         obj = os.path.join(_BUILD, os.path.basename(src) + ".o")
         stamp = obj + ".sha1"
-        dg = _digest(src, common)
+        dg = _digest(src, common + (["precise"] if os.path.basename(src) in PRECISE else []))
         objs.append(obj)
         if not force and os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == dg:
             continue
@@ -71,7 +73,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
                    "-DTORCH_API_INCLUDE_EXTENSION_H", "-DNDEBUG", "-Wno-deprecated-declarations",
                    "-I/usr/local/cuda/include"] + _include_flags() + ["-c", src, "-o", obj]
         else:
-            cmd = [nvcc] + common + ["-c", src, "-o", obj]
+            flags = [f for f in common if not (f == "--use_fast_math" and os.path.basename(src) in PRECISE)]
+            cmd = [nvcc] + flags + ["-c", src, "-o", obj]
         jobs.append((cmd, stamp, dg, src))
 
     def run(job):
