@@ -6,6 +6,8 @@
 #include <cuda_bf16.h>
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "seqmix.h"
 
@@ -151,6 +153,76 @@ __global__ void __launch_bounds__(256) conv_qknorm_rope_append_kernel(ConvQkPara
   for (int c = threadIdx.x; c < Cv; c += blockDim.x) stf(vo + c, buf[Cq + Ck + c]);
 }
 
+// Two channels per thread (every rotation pair, 4- or 8-byte accesses): taken when value size and row strides are even.
+template <typename T> __device__ __forceinline__ float2 ld2(const T* p);
+template <> __device__ __forceinline__ float2 ld2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 ld2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename T> __device__ __forceinline__ void st2(T* p, float a, float b);
+template <> __device__ __forceinline__ void st2<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+template <> __device__ __forceinline__ void st2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv_qknorm_rope_append_pair_kernel(ConvQkParams p) {
+  extern __shared__ float buf[];      // [Cq + Ck + Cv] convolved row
+  __shared__ float red[32];
+  const int b = blockIdx.y, t = blockIdx.x;
+  if (t >= p.q_len[b]) return;
+  const int Cq = p.n_q * p.D, Ck = p.n_kv * p.D, Cv = p.n_kv * p.Dv, C = Cq + Ck + Cv, K = p.K;
+  const bool has_ctx = p.ctx_len[b] > 0;
+  const T* u0 = (const T*)p.p + (long long)b * p.p_sb;
+  const T* sl = (const T*)p.state + (long long)p.lines[b] * (K - 1) * C;
+  float sq = 0.f, sk = 0.f;
+  for (int c = 2 * threadIdx.x; c < C; c += 2 * blockDim.x) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = 0; j < K; ++j) {
+      const int i = t - K + 1 + j;
+      float2 v = make_float2(0.f, 0.f);
+      if (i >= 0) v = ld2(u0 + (long long)i * p.p_st + c);
+      else if (has_ctx) v = ld2(sl + (long long)(K - 1 + i) * C + c);
+      a0 += p.conv_w[(long long)c * K + j] * v.x;
+      a1 += p.conv_w[(long long)(c + 1) * K + j] * v.y;
+    }
+    buf[c] = a0;
+    buf[c + 1] = a1;
+    const float ss = a0 * a0 + a1 * a1;
+    if (c < Cq) sq += ss;
+    else if (c < Cq + Ck) sk += ss;
+  }
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);
+  const float rq = 1.f / sqrtf(sq / (float)Cq + p.eps);
+  const float rk = Ck ? 1.f / sqrtf(sk / (float)Ck + p.eps) : 0.f;
+  const long long tok = (long long)b * p.T + t;
+  const float* cs = p.cos + tok * (p.R / 2);
+  const float* sn = p.sin + tok * (p.R / 2);
+  const int pos = p.ctx_len[b] + t;
+  long long slot = 0;
+  if (p.n_kv) slot = (long long)p.block_table[(long long)b * p.max_blocks + pos / p.page] * p.page + pos % p.page;
+  T* qo = (T*)p.q_out + tok * Cq;
+  T* ko = (T*)p.k_cache + slot * Ck;
+  T* vo = (T*)p.v_cache + slot * Cv;
+  for (int c = 2 * threadIdx.x; c < Cq + Ck; c += 2 * blockDim.x) {
+    const bool isq = c < Cq;
+    const int cc = isq ? c : c - Cq;
+    const float r = isq ? rq : rk;
+    const float* nw = isq ? p.q_norm_w : p.k_norm_w;
+    const int d = cc % p.D;
+    float a = buf[c] * r * nw[cc], bb = buf[c + 1] * r * nw[cc + 1];
+    if (d < p.R) {
+      const float co = cs[d >> 1], si = sn[d >> 1];
+      const float ra = a * co - bb * si, rb = bb * co + a * si;
+      a = ra;
+      bb = rb;
+    }
+    st2((isq ? qo : ko) + cc, a, bb);
+  }
+  for (int c = 2 * threadIdx.x; c < Cv; c += 2 * blockDim.x) st2(vo + c, buf[Cq + Ck + c], buf[Cq + Ck + c + 1]);
+}
+
 // ---- soft-capped kept-prefix sliding-window attention over the paged cache ---------------------------------------------------
 template <typename T> struct Vec;                     // 16-byte vectors of the activation type
 template <> struct Vec<float> { static constexpr int N = 4; };
@@ -183,11 +255,11 @@ constexpr int ATT_VPL = SEQMIX_MAX_VDIM / 32;      // value channels per lane
 // SPLIT = false: warp w of a block owns query blockIdx.x * 4 + w.  SPLIT = true: the four warps share query blockIdx.x, warp w takes
 // key chunks w, w + 4, ... and the partial (max, sum, acc) are merged through shared memory (few queries, long ranges: decode).
 template <typename T, bool SPLIT>
-__global__ void __launch_bounds__(ATT_WARPS * 32) paged_window_attention_kernel(WindowAttnParams p) {
-  extern __shared__ float smem[];      // [ATT_WARPS][D] scaled queries, then (SPLIT) [ATT_WARPS][Dv + 2] partials
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(SPLIT ? 512 : ATT_WARPS * 32) paged_window_attention_kernel(WindowAttnParams p) {
+  extern __shared__ float smem[];      // [warps][D] scaled queries, then (SPLIT) [warps][Dv + 2] partials
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const long long nq = (long long)p.B * p.T * p.Hq;
-  const long long qi = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * ATT_WARPS + warp;
+  const long long qi = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * nwarps + warp;
   const bool in_range = qi < nq;
   const int h = in_range ? (int)(qi % p.Hq) : 0;
   const long long tok = in_range ? qi / p.Hq : 0;
@@ -212,7 +284,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_window_attention_kernel(
 #pragma unroll
   for (int i = 0; i < ATT_VPL; ++i) acc[i] = 0.f;
   const int nchunks = (n + 31) / 32;
-  for (int ch = SPLIT ? warp : 0; ch < nchunks; ch += SPLIT ? ATT_WARPS : 1) {
+  for (int ch = SPLIT ? warp : 0; ch < nchunks; ch += SPLIT ? nwarps : 1) {
     const int idx = ch * 32 + lane;
     float s = -INFINITY;
     long long row = 0;
@@ -242,7 +314,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_window_attention_kernel(
     }
   }
   if (SPLIT) {
-    float* part = smem + ATT_WARPS * D + warp * (Dv + 2);
+    float* part = smem + nwarps * D + warp * (Dv + 2);
 #pragma unroll
     for (int i = 0; i < ATT_VPL; ++i) {
       const int dv = lane + 32 * i;
@@ -252,12 +324,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_window_attention_kernel(
     __syncthreads();
     if (warp != 0) return;
     float M = -INFINITY;
-    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, smem[ATT_WARPS * D + w * (Dv + 2) + Dv]);
+    for (int w = 0; w < nwarps; ++w) M = fmaxf(M, smem[nwarps * D + w * (Dv + 2) + Dv]);
     l = 0.f;
 #pragma unroll
     for (int i = 0; i < ATT_VPL; ++i) acc[i] = 0.f;
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      const float* pw = smem + ATT_WARPS * D + w * (Dv + 2);
+    for (int w = 0; w < nwarps; ++w) {
+      const float* pw = smem + nwarps * D + w * (Dv + 2);
       const float f = pw[Dv] == -INFINITY ? 0.f : expf(pw[Dv] - M);
       l += pw[Dv + 1] * f;
 #pragma unroll
@@ -281,21 +353,215 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) paged_window_attention_kernel(
   }
 }
 
+// ---- the same attention on tensor cores (bf16, head sizes 64 / 128): prompt portions ------------------------------------------
+// Block = 64 queries of one (row, head), 4 warps x 16 query rows.  Keys and values come in tiles of 64 from the paged cache into
+// shared memory; S = Q K^T and O += P V run on mma.sync m16n8k16 with fp32 accumulators; scale, soft cap, mask and the online
+// softmax are fp32 on the accumulator fragments; P is rounded to bf16 for the second product.  Tiles cover the kept first tokens
+// that the block's window no longer reaches, then the window itself; the per-element mask is the exact visibility rule.
+constexpr int MMA_MT = 64, MMA_KT = 64;
+
+__device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128) paged_window_attention_mma_kernel(WindowAttnParams p) {
+  constexpr int KS = D + 8, VS = DV + 8, STAGE = MMA_KT * (KS + VS);
+  extern __shared__ __align__(16) unsigned char mma_smem[];       // two stages of [64][KS] keys + [64][VS] values
+  __nv_bfloat16* stage0 = reinterpret_cast<__nv_bfloat16*>(mma_smem);
+  const int h = blockIdx.y, b = blockIdx.z, t0 = blockIdx.x * MMA_MT;
+  const int qn = p.q_len[b];
+  if (t0 >= qn) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int g = h / (p.Hq / p.G), ctx = p.ctx_len[b];
+  const int r0 = t0 + warp * 16 + gid, r1 = r0 + 8;            // this thread's two query rows (token index in the row of the batch)
+  const int pos0 = ctx + r0, pos1 = ctx + r1;
+  uint32_t qa[D / 16][4];
+  {
+    const __nv_bfloat16* qb = (const __nv_bfloat16*)p.q + ((long long)b * p.T * p.Hq + h) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int col = ks * 16 + tig * 2;
+      qa[ks][0] = r0 < p.T ? *reinterpret_cast<const uint32_t*>(qb + (long long)r0 * p.Hq * D + col) : 0u;
+      qa[ks][1] = r1 < p.T ? *reinterpret_cast<const uint32_t*>(qb + (long long)r1 * p.Hq * D + col) : 0u;
+      qa[ks][2] = r0 < p.T ? *reinterpret_cast<const uint32_t*>(qb + (long long)r0 * p.Hq * D + col + 8) : 0u;
+      qa[ks][3] = r1 < p.T ? *reinterpret_cast<const uint32_t*>(qb + (long long)r1 * p.Hq * D + col + 8) : 0u;
+    }
+  }
+  float o[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int p_first = ctx + t0, p_last = ctx + min(t0 + MMA_MT, qn) - 1;
+  const int lo = p.window > 0 ? max(p_first - p.window + 1, 0) : 0;
+  const int nA = p.window > 0 ? min(p.keep_first, lo) : 0;
+  const int* table = p.block_table + (long long)b * p.max_blocks;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)p.k_cache;
+  const __nv_bfloat16* vc = (const __nv_bfloat16*)p.v_cache;
+  const int ntA = (nA + MMA_KT - 1) / MMA_KT, ntB = (p_last + 1 - lo + MMA_KT - 1) / MMA_KT, ntiles = ntA + ntB;
+  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const int warp_pos_lo = ctx + t0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
+  // tile i covers keys [j0, min(j0 + 64, end)): first the kept tokens below the window, then the window
+  auto tile_range = [&](int i, int& j0, int& end) {
+    if (i < ntA) { j0 = i * MMA_KT; end = nA; }
+    else { j0 = lo + (i - ntA) * MMA_KT; end = p_last + 1; }
+  };
+  // all copies of a tile are issued back to back (16-byte cp.async, zero fill past `end`), one commit group per tile
+  auto load_tile = [&](int i) {
+    int j0, end;
+    tile_range(i, j0, end);
+    __nv_bfloat16* Kd = stage0 + (i & 1) * STAGE;
+    __nv_bfloat16* Vd = Kd + MMA_KT * KS;
+#pragma unroll
+    for (int k = 0; k < MMA_KT * (D / 8) / 128; ++k) {
+      const int c = threadIdx.x + 128 * k, r = c / (D / 8), ch = c % (D / 8), j = j0 + r, jj = min(j, end - 1);
+      const long long row = ((long long)table[jj / p.page] * p.page + jj % p.page) * p.G + g;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Kd + r * KS + ch * 8);
+      const int nbytes = j < end ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(kc + row * D + ch * 8), "r"(nbytes));
+    }
+#pragma unroll
+    for (int k = 0; k < MMA_KT * (DV / 8) / 128; ++k) {
+      const int c = threadIdx.x + 128 * k, r = c / (DV / 8), ch = c % (DV / 8), j = j0 + r, jj = min(j, end - 1);
+      const long long row = ((long long)table[jj / p.page] * p.page + jj % p.page) * p.G + g;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Vd + r * VS + ch * 8);
+      const int nbytes = j < end ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(vc + row * DV + ch * 8), "r"(nbytes));
+    }
+    asm volatile("cp.async.commit_group;");
+  };
+  load_tile(0);
+  for (int i = 0; i < ntiles; ++i) {
+    if (i + 1 < ntiles) {
+      load_tile(i + 1);                   // lands while tile i is computed
+      asm volatile("cp.async.wait_group 1;");
+    } else {
+      asm volatile("cp.async.wait_group 0;");
+    }
+    __syncthreads();
+    int j0, end;
+    tile_range(i, j0, end);
+    const __nv_bfloat16* Ks = stage0 + (i & 1) * STAGE;
+    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(Ks + MMA_KT * KS);
+    {
+      float sc[MMA_KT / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < MMA_KT / 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+#pragma unroll
+        for (int nt = 0; nt < MMA_KT / 8; ++nt) {
+          const __nv_bfloat16* kp = Ks + (nt * 8 + gid) * KS + ks * 16 + tig * 2;
+          const uint32_t bb[2] = {*reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8)};
+          mma_bf16_16816(sc[nt], qa[ks], bb);
+        }
+      // a tile that every row of this warp sees completely needs no mask
+      const bool full = j0 + MMA_KT <= end && j0 + MMA_KT - 1 <= warp_pos_lo &&
+                        (p.window <= 0 || warp_pos_hi - j0 < p.window || j0 + MMA_KT <= p.keep_first);
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < MMA_KT / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = sc[nt][e] * p.scale;
+          if (p.softcap > 0.f) v = p.softcap * tanh_fast(v * inv_cap);
+          if (!full) {
+            const int j = j0 + nt * 8 + tig * 2 + (e & 1);
+            const int pos = (e < 2) ? pos0 : pos1;
+            const bool see = j < end && j <= pos && (p.window <= 0 || pos - j < p.window || j < p.keep_first);
+            v = see ? v : -INFINITY;
+          }
+          sc[nt][e] = v;
+          if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
+      const float c0 = m0 == -INFINITY ? 0.f : __expf(m0 - base0), c1 = m1 == -INFINITY ? 0.f : __expf(m1 - base1);
+      m0 = n0; m1 = n1;
+      float s0 = 0.f, s1 = 0.f;
+      uint32_t pa[MMA_KT / 16][4];
+#pragma unroll
+      for (int nt = 0; nt < MMA_KT / 8; ++nt) {
+        const float e0 = __expf(sc[nt][0] - base0), e1 = __expf(sc[nt][1] - base0);
+        const float e2 = __expf(sc[nt][2] - base1), e3 = __expf(sc[nt][3] - base1);
+        s0 += e0 + e1;
+        s1 += e2 + e3;
+        pa[nt >> 1][(nt & 1) * 2] = pack_bf16(e0, e1);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e2, e3);
+      }
+      l0 = l0 * c0 + s0;
+      l1 = l1 * c1 + s1;
+#pragma unroll
+      for (int i2 = 0; i2 < DV / 8; ++i2) { o[i2][0] *= c0; o[i2][1] *= c0; o[i2][2] *= c1; o[i2][3] *= c1; }
+#pragma unroll
+      for (int kk = 0; kk < MMA_KT / 16; ++kk)
+#pragma unroll
+        for (int nv = 0; nv < DV / 8; nv += 2) {
+          // four 8x8 blocks of V (keys kk*16 .. +15, value channels nv*8 .. +15), transposed on load: B fragments of two n-tiles
+          const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, col = (nv + (lane >> 4)) * 8;
+          const uint32_t addr = vs_base + (uint32_t)((row * VS + col) * 2);
+          uint32_t v0, v1, v2, v3;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(addr));
+          const uint32_t ba[2] = {v0, v1}, bb[2] = {v2, v3};
+          mma_bf16_16816(o[nv], pa[kk], ba);
+          mma_bf16_16816(o[nv + 1], pa[kk], bb);
+        }
+    }
+    __syncthreads();                      // the stage is free for tile i + 2
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
+  __nv_bfloat16* ob = (__nv_bfloat16*)p.out + ((long long)b * p.T * p.Hq + h) * DV;
+  const __nv_bfloat16* gb = p.gate ? (const __nv_bfloat16*)p.gate + (long long)b * p.g_sb + (long long)h * DV : nullptr;
+#pragma unroll
+  for (int nv = 0; nv < DV / 8; ++nv) {
+    const int col = nv * 8 + tig * 2;
+    if (r0 < qn) {
+      float a = o[nv][0] * i0, c = o[nv][1] * i0;
+      if (gb) {
+        a *= sigmoidf_acc(__bfloat162float(gb[(long long)r0 * p.g_st + col]));
+        c *= sigmoidf_acc(__bfloat162float(gb[(long long)r0 * p.g_st + col + 1]));
+      }
+      *reinterpret_cast<uint32_t*>(ob + (long long)r0 * p.Hq * DV + col) = pack_bf16(a, c);
+    }
+    if (r1 < qn) {
+      float a = o[nv][2] * i1, c = o[nv][3] * i1;
+      if (gb) {
+        a *= sigmoidf_acc(__bfloat162float(gb[(long long)r1 * p.g_st + col]));
+        c *= sigmoidf_acc(__bfloat162float(gb[(long long)r1 * p.g_st + col + 1]));
+      }
+      *reinterpret_cast<uint32_t*>(ob + (long long)r1 * p.Hq * DV + col) = pack_bf16(a, c);
+    }
+  }
+}
+
 // ---- Mamba-2 recurrence with a carried state ----------------------------------------------------------------------------------
+// Block = one (row, head, 16 head channels); 8 lanes split the state axis of a channel and hold their share of S in registers.  Time
+// runs in rounds of 16 steps: the B / C / x / dt / z values of round r + 1 are fetched into registers while round r is computed out
+// of shared memory, so the global-load latency is paid once per sequence instead of once per round.
 constexpr int SCAN_PT = 16;      // head channels per block
 constexpr int SCAN_NS = 8;       // lanes that split the state axis for one channel
 constexpr int SCAN_TT = 16;      // time steps staged per round
-constexpr int SCAN_NPT = SEQMIX_MAX_STATE / SCAN_NS;
+constexpr int SCAN_THREADS = SCAN_PT * SCAN_NS;
 
-template <typename T>
-__global__ void __launch_bounds__(SCAN_PT* SCAN_NS) ssd_scan_kernel(SsdScanParams p) {
+// NB = ceil(N / 128): state values per lane = 16 * NB, staged B / C values per thread and round = 16 * NB
+template <typename T, int NB>
+__global__ void __launch_bounds__(SCAN_THREADS, NB == 1 ? 4 : 2) ssd_scan_kernel(SsdScanParams p) {
   extern __shared__ float sm[];
+  constexpr int NPT = 16 * NB;             // state values per lane: n = ns * NPT + i
+  constexpr int NP = 160 * NB;             // padded row of staged B / C: 4 floats after every 16, so that the 8 lanes' float4 reads miss each other
   const int N = p.N, P = p.P;
-  float* Bs = sm;                          // [TT][N]
-  float* Cs = Bs + SCAN_TT * N;            // [TT][N]
-  float* xs = Cs + SCAN_TT * N;            // [TT][PT]
+  float* Bs = sm;                          // [TT][NP], zero past N
+  float* Cs = Bs + SCAN_TT * NP;           // [TT][NP]
+  float* xs = Cs + SCAN_TT * NP;           // [TT][PT]
   float* ys = xs + SCAN_TT * SCAN_PT;      // [TT][PT]
-  float* dts = ys + SCAN_TT * SCAN_PT;     // [TT]
+  float* zs = ys + SCAN_TT * SCAN_PT;      // [TT][PT]
+  float* dts = zs + SCAN_TT * SCAN_PT;     // [TT]
   float* dAs = dts + SCAN_TT;              // [TT]
   const int b = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * SCAN_PT;
   const int n_tok = p.q_len[b];
@@ -306,66 +572,94 @@ __global__ void __launch_bounds__(SCAN_PT* SCAN_NS) ssd_scan_kernel(SsdScanParam
   const int g = h / (p.nh / p.G);
   const int inner = p.nh * P, Cd = inner + 2 * p.G * N;
   float* Sg = p.state + ((long long)p.lines[b] * p.nh + h) * N * P;
-  float S[SCAN_NPT];
+  float S[NPT];
   const bool has_ctx = p.ctx_len[b] > 0;
 #pragma unroll
-  for (int i = 0; i < SCAN_NPT; ++i) {
-    const int n = ns + SCAN_NS * i;
+  for (int i = 0; i < NPT; ++i) {
+    const int n = ns * NPT + i;
     S[i] = (has_ctx && pok && n < N) ? Sg[(long long)n * P + pc] : 0.f;
   }
   const float negA = -expf(p.A_log[h]), dtb = p.dt_bias[h], Dh = p.D_skip[h];
   const float* xrow = p.xBC + (long long)b * p.T * Cd;
   const T* dtp = (const T*)p.dt_raw + (long long)b * p.dt_sb + h;
+  const T* zp = (const T*)p.z + (long long)b * p.z_sb + h * P;
+  // staging registers: element (t, n) with n = tid + 128 * k for B / C, element i = tid + 128 * k of the [TT][PT] tile for x / z
+  float rb[NPT], rc[NPT], rx[2], rz[2], rdt = 0.f;
+  auto fetch = [&](int t0) {
+    const int tt = min(SCAN_TT, n_tok - t0);
+#pragma unroll
+    for (int t = 0; t < SCAN_TT; ++t)
+#pragma unroll
+      for (int k = 0; k < NB; ++k) {
+        const int n = tid + SCAN_THREADS * k;
+        const bool ok = t < tt && n < N;
+        const float* r = xrow + (long long)(t0 + t) * Cd + inner + g * N + n;
+        rb[t * NB + k] = ok ? r[0] : 0.f;
+        rc[t * NB + k] = ok ? r[p.G * N] : 0.f;
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = tid + SCAN_THREADS * k, t = i / SCAN_PT, c = p0 + i % SCAN_PT;
+      const bool ok = t < tt && c < P;
+      rx[k] = ok ? xrow[(long long)(t0 + t) * Cd + h * P + c] : 0.f;
+      rz[k] = ok ? ldf(zp + (long long)(t0 + t) * p.z_st + c) : 0.f;
+    }
+    rdt = tid < tt ? ldf(dtp + (long long)(t0 + tid) * p.dt_st) : 0.f;
+  };
+  fetch(0);
   for (int t0 = 0; t0 < n_tok; t0 += SCAN_TT) {
     const int tt = min(SCAN_TT, n_tok - t0);
-    __syncthreads();
-    for (int i = tid; i < tt * N; i += blockDim.x) {
-      const int t = i / N, n = i % N;
-      const float* r = xrow + (long long)(t0 + t) * Cd + inner + g * N + n;
-      Bs[t * N + n] = r[0];
-      Cs[t * N + n] = r[p.G * N];
-    }
-    for (int i = tid; i < tt * SCAN_PT; i += blockDim.x) {
-      const int t = i / SCAN_PT, c = p0 + i % SCAN_PT;
-      xs[i] = c < P ? xrow[(long long)(t0 + t) * Cd + h * P + c] : 0.f;
-    }
-    if (tid < tt) {
-      const float v = ldf(dtp + (long long)(t0 + tid) * p.dt_st) + dtb;
+    __syncthreads();                      // the previous round's readers are done with the tiles
+#pragma unroll
+    for (int t = 0; t < SCAN_TT; ++t)
+#pragma unroll
+      for (int k = 0; k < NB; ++k) {
+        const int n = tid + SCAN_THREADS * k, at = t * NP + n + (n >> 4) * 4;
+        Bs[at] = rb[t * NB + k];
+        Cs[at] = rc[t * NB + k];
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) { xs[tid + SCAN_THREADS * k] = rx[k]; zs[tid + SCAN_THREADS * k] = rz[k]; }
+    if (tid < SCAN_TT) {
+      const float v = rdt + dtb;
       const float dt = v > 20.f ? v : log1pf(expf(v));
       dts[tid] = dt;
       dAs[tid] = expf(negA * dt);
     }
     __syncthreads();
+    if (t0 + SCAN_TT < n_tok) fetch(t0 + SCAN_TT);      // in flight while this round computes
     for (int t = 0; t < tt; ++t) {
       const float dA = dAs[t], dx = dts[t] * xs[t * SCAN_PT + pl];
-      const float* Bt = Bs + t * N;
-      const float* Ct = Cs + t * N;
-      float y = 0.f;
+      const float4* Bt = reinterpret_cast<const float4*>(Bs + t * NP) + ns * (NPT * 5 / 16);
+      const float4* Ct = reinterpret_cast<const float4*>(Cs + t * NP) + ns * (NPT * 5 / 16);
+      float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < SCAN_NPT; ++i) {
-        const int n = ns + SCAN_NS * i;
-        if (n < N) {
-          S[i] = dA * S[i] + dx * Bt[n];
-          y += S[i] * Ct[n];
-        }
+      for (int q = 0; q < NPT / 4; ++q) {          // B and C are zero past N: those S stay zero and add nothing
+        const float4 bv = Bt[q + (q >> 2)], cv = Ct[q + (q >> 2)];
+        S[4 * q] = dA * S[4 * q] + dx * bv.x;
+        S[4 * q + 1] = dA * S[4 * q + 1] + dx * bv.y;
+        S[4 * q + 2] = dA * S[4 * q + 2] + dx * bv.z;
+        S[4 * q + 3] = dA * S[4 * q + 3] + dx * bv.w;
+        y0 += S[4 * q] * cv.x + S[4 * q + 2] * cv.z;
+        y1 += S[4 * q + 1] * cv.y + S[4 * q + 3] * cv.w;
       }
+      float y = y0 + y1;
 #pragma unroll
       for (int o = SCAN_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
       if (ns == 0) ys[t * SCAN_PT + pl] = y + Dh * xs[t * SCAN_PT + pl];
     }
     __syncthreads();
-    for (int i = tid; i < tt * SCAN_PT; i += blockDim.x) {
+    for (int i = tid; i < tt * SCAN_PT; i += SCAN_THREADS) {
       const int t = i / SCAN_PT, c = p0 + i % SCAN_PT;
       if (c < P) {
-        const long long tok = (long long)b * p.T + t0 + t;
-        const float zv = ldf((const T*)p.z + (long long)b * p.z_sb + (long long)(t0 + t) * p.z_st + h * P + c);
-        p.y[tok * inner + h * P + c] = ys[i] * (zv * sigmoidf_acc(zv));
+        const float zv = zs[i];
+        p.y[((long long)b * p.T + t0 + t) * inner + h * P + c] = ys[i] * (zv * sigmoidf_acc(zv));
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < SCAN_NPT; ++i) {
-    const int n = ns + SCAN_NS * i;
+  for (int i = 0; i < NPT; ++i) {
+    const int n = ns * NPT + i;
     if (pok && n < N) Sg[(long long)n * P + pc] = S[i];
   }
 }
@@ -441,25 +735,47 @@ void conv_qknorm_rope_append_launch(const ConvQkParams& p, bool lp, cudaStream_t
   if (p.B <= 0 || p.T <= 0) return;
   const size_t smem = sizeof(float) * (size_t)(p.n_q * p.D + p.n_kv * (p.D + p.Dv));
   dim3 grid(p.T, p.B);
+  const size_t esz = lp ? 2 : 4;
+  const bool pairs = p.Dv % 2 == 0 && p.R % 2 == 0 && p.p_sb % 2 == 0 && p.p_st % 2 == 0 && ((uintptr_t)p.p % (2 * esz)) == 0;
+  auto go = [&](auto kernel) {
+    opt_in_smem(kernel, smem);
+    kernel<<<grid, 256, smem, st>>>(p);
+  };
   if (lp) {
-    opt_in_smem(conv_qknorm_rope_append_kernel<__nv_bfloat16>, smem);
-    conv_qknorm_rope_append_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(p);
+    if (pairs) go(conv_qknorm_rope_append_pair_kernel<__nv_bfloat16>); else go(conv_qknorm_rope_append_kernel<__nv_bfloat16>);
   } else {
-    opt_in_smem(conv_qknorm_rope_append_kernel<float>, smem);
-    conv_qknorm_rope_append_kernel<float><<<grid, 256, smem, st>>>(p);
+    if (pairs) go(conv_qknorm_rope_append_pair_kernel<float>); else go(conv_qknorm_rope_append_kernel<float>);
   }
 }
 
 void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStream_t st) {
   const long long nq = (long long)p.B * p.T * p.Hq;
   if (nq <= 0) return;
+  if (lp && p.T >= 16 && (p.D == 64 || p.D == 128) && (p.Dv == 64 || p.Dv == 128)) {
+    // prompt portions in bf16: tensor-core kernel
+    dim3 grid((p.T + MMA_MT - 1) / MMA_MT, p.Hq, p.B);
+    const size_t smem = 2 * (size_t)MMA_KT * (p.D + 8 + p.Dv + 8) * sizeof(__nv_bfloat16);
+    auto go = [&](auto kernel) {
+      opt_in_smem(kernel, smem);
+      kernel<<<grid, 128, smem, st>>>(p);
+    };
+    if (p.D == 64 && p.Dv == 64) go(paged_window_attention_mma_kernel<64, 64>);
+    else if (p.D == 64) go(paged_window_attention_mma_kernel<64, 128>);
+    else if (p.Dv == 64) go(paged_window_attention_mma_kernel<128, 64>);
+    else go(paged_window_attention_mma_kernel<128, 128>);
+    return;
+  }
   // few queries (decode steps): one block per query, its warps split the keys; otherwise one warp per query
   const bool split = nq <= 2LL * kNumSMs * 4;
-  const size_t smem = sizeof(float) * (size_t)(ATT_WARPS * p.D + (split ? ATT_WARPS * (p.Dv + 2) : 0));
+  // split mode: one warp per 64 visible keys (bounded by the window or by the pages a row can hold), 4 to 16 warps
+  long long span = (long long)p.max_blocks * p.page;
+  if (p.window > 0) span = std::min<long long>(span, (long long)p.window + p.keep_first);
+  const int nwarps = split ? (int)std::min<long long>(16, std::max<long long>(ATT_WARPS, (span + 63) / 64)) : ATT_WARPS;
+  const size_t smem = sizeof(float) * (size_t)(nwarps * p.D + (split ? nwarps * (p.Dv + 2) : 0));
   const unsigned grid = (unsigned)(split ? nq : (nq + ATT_WARPS - 1) / ATT_WARPS);
   auto go = [&](auto kernel) {
     opt_in_smem(kernel, smem);
-    kernel<<<grid, ATT_WARPS * 32, smem, st>>>(p);
+    kernel<<<grid, nwarps * 32, smem, st>>>(p);
   };
   if (lp) {
     if (split) go(paged_window_attention_kernel<__nv_bfloat16, true>); else go(paged_window_attention_kernel<__nv_bfloat16, false>);
@@ -470,14 +786,16 @@ void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStrea
 
 void ssd_scan_launch(const SsdScanParams& p, bool lp, cudaStream_t st) {
   if (p.B <= 0 || p.T <= 0) return;
-  const size_t smem = sizeof(float) * (size_t)(2 * SCAN_TT * p.N + 2 * SCAN_TT * SCAN_PT + 2 * SCAN_TT);
+  const size_t smem = sizeof(float) * (size_t)(2 * SCAN_TT * 160 * (p.N <= 128 ? 1 : 2) + 3 * SCAN_TT * SCAN_PT + 2 * SCAN_TT);
   dim3 grid((p.P + SCAN_PT - 1) / SCAN_PT, p.nh, p.B);
-  if (lp) {
-    opt_in_smem(ssd_scan_kernel<__nv_bfloat16>, smem);
-    ssd_scan_kernel<__nv_bfloat16><<<grid, SCAN_PT * SCAN_NS, smem, st>>>(p);
+  auto go = [&](auto kernel) {
+    opt_in_smem(kernel, smem);
+    kernel<<<grid, SCAN_THREADS, smem, st>>>(p);
+  };
+  if (p.N <= 128) {
+    if (lp) go(ssd_scan_kernel<__nv_bfloat16, 1>); else go(ssd_scan_kernel<float, 1>);
   } else {
-    opt_in_smem(ssd_scan_kernel<float>, smem);
-    ssd_scan_kernel<float><<<grid, SCAN_PT * SCAN_NS, smem, st>>>(p);
+    if (lp) go(ssd_scan_kernel<__nv_bfloat16, 2>); else go(ssd_scan_kernel<float, 2>);
   }
 }
 

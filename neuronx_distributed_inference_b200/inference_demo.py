@@ -109,7 +109,11 @@ def setup_run_parser(p: argparse.ArgumentParser):
     p.add_argument("--divergence-difference-tol", type=float, default=0.001)
     p.add_argument("--tol-map", type=str)
     p.add_argument("--num-tokens-to-check", type=int)
-    p.add_argument("--prompt", dest="prompts", type=str, action="append", required=True)
+    p.add_argument("--prompt", dest="prompts", type=str, action="append")
+    p.add_argument("--prompt-token-ids", dest="prompt_token_ids", type=str, action="append",
+                   help="a prompt as comma-separated token ids (repeatable), for checkpoints that ship no tokenizer: the prompts run through "
+                        "the paged continuous-batching engine (runtime/scheduler.py) and the generated ids are printed")
+    p.add_argument("--max-step-tokens", type=int, default=256, help="--prompt-token-ids: token budget of one engine step (chunked prefill)")
     p.add_argument("--top-k", type=int, default=1)
     p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--temperature", type=float, default=1.0)
@@ -385,10 +389,37 @@ def run_generation(model, tokenizer, prompts, gc, draft_model=None, rank=0):
     return texts
 
 
+def run_token_ids(args):
+    """Tokenizer-less generation: ``--prompt-token-ids`` through ``PagedBatchEngine.generate`` (greedy unless ``--do-sample``)."""
+    from .config import OnDeviceSamplingConfig
+    from .runtime.scheduler import build_engine
+    prompts = [[int(t) for t in p.replace(" ", "").split(",") if t] for p in args.prompt_token_ids]
+    new = args.max_new_tokens or 16
+    live = min(len(prompts), args.batch_size or 4)
+    page = args.pa_block_size or 64
+    need = sum(-(-(len(p) + new) // page) * page for p in sorted(prompts, key=len, reverse=True)[:live])
+    sampling = OnDeviceSamplingConfig(do_sample=bool(args.do_sample), top_k=args.top_k if args.do_sample else 1, top_p=args.top_p,
+                                      temperature=args.temperature)
+    if args.on_device_sampling is False and args.do_sample:
+        raise ValueError("--prompt-token-ids samples on the device")
+    dtype = str(args.torch_dtype).replace("torch.", "") if args.torch_dtype is not None else "bfloat16"
+    engine = build_engine(args.model_path, dtype, max_tokens=max(need, args.seq_len or 0), max_requests=max(live, 1), page_size=page,
+                          device="cpu" if args.on_cpu else None, max_portion=args.max_context_length, sampling=sampling)
+    outs = engine.generate(prompts, new, max_step_tokens=args.max_step_tokens)
+    print("Generated outputs:")
+    for i, o in enumerate(outs):
+        print(f"Output {i}: {','.join(str(t) for t in o)}")
+    return outs
+
+
 def main(argv=None):
     argv = sys.argv[1:] if argv is None else argv
     logging.basicConfig(level=logging.INFO)
     args = parse_args(argv)
+    if getattr(args, "prompt_token_ids", None):
+        return run_token_ids(args)
+    if not args.prompts:
+        raise SystemExit("inference_demo: give --prompt (text, needs the checkpoint's tokenizer) or --prompt-token-ids")
     _maybe_relaunch(args, argv)
     model_cls = get_model_cls(args.model_type, args.task_type)
     run_inference(model_cls, args)

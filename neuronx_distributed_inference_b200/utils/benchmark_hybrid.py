@@ -183,6 +183,14 @@ def kernel_table(size, batch, prompt, hbm_gbs):
         qn, kn = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
         run(f"{phase}: conv_qknorm_rope_append", lambda: ops.conv_qknorm_rope_append(p, cw, st, lines, ctx, ql, qn, kn, 1e-5, H, G, D, D, cos, sin, kc, vc, table),
             R * C * 2 * 2)
+        if phase == "prefill":
+            qkv = torch.randn(B, T, C, device=dev, dtype=bf)
+            cf, sf = torch.randn(B, T, D // 2, device=dev), torch.randn(B, T, D // 2, device=dev)
+            kcl, vcl = (torch.zeros(B + 1, G, T, D, device=dev, dtype=bf) for _ in range(2))
+            posl = torch.arange(T, dtype=torch.int32, device=dev).view(1, T).expand(B, T).contiguous()
+            if ops.rope_kv_split_append(qkv, cf, sf, kcl, vcl, lines, posl, H, G, D) is not None:
+                run("prefill: rope_kv_split_append (Llama path: split + rotate + cache write, no convolution / row norm)",
+                    lambda: ops.rope_kv_split_append(qkv, cf, sf, kcl, vcl, lines, posl, H, G, D), R * C * 2 * 2 + R * 2 * G * D * 2)
         run(f"{phase}: short_conv_update (q|k|v)", lambda: ops.short_conv_update(p[..., :C], st, lines, ctx, ql), B * (K - 1) * C * 2 * 2)
         q = torch.randn(B, T, H, D, device=dev, dtype=bf)
         keys = ctx0 + T

@@ -383,3 +383,29 @@ def test_gpu_kernels_match_definitions_on_ragged_rows():
         d = ops.ssd_scan(xBC.to(dev), pz.to(dev)[..., inner:inner + nh], pz.to(dev)[..., :inner], Al.to(dev), db.to(dev), Dk.to(dev), S2,
                          lines.to(dev), ctx.to(dev), ql.to(dev), nh, P, N, G)
         assert torch.allclose(c * live, d.cpu() * live, atol=1e-4, rtol=1e-4) and torch.allclose(S1, S2.cpu(), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,Dv", [(64, 64), (128, 128), (64, 128), (128, 64)])
+def test_gpu_tensor_core_attention_on_prompt_portions(D, Dv):
+    """bf16 portions of 16+ tokens take the mma kernel: ragged rows that start mid-sequence, scattered pages, window and kept-token
+    edges inside and across key tiles, one dominant far key per row."""
+    from neuronx_distributed_inference_b200 import ops
+    from neuronx_distributed_inference_b200.ops import reference as ref
+    g = torch.Generator().manual_seed(D + Dv)
+    B, T, H, G, page = 3, 150, 4, 2, 16
+    ctx, ql = torch.tensor([0, 70, 129]), torch.tensor([150, 93, 17])
+    nblk = -(-(int((ctx + ql).max())) // page)
+    table = torch.stack([torch.randperm(B * nblk, generator=g)[b * nblk:(b + 1) * nblk] for b in range(B)]).int()
+    kc, vc = torch.randn(B * nblk, page, G, D, generator=g) * 0.5, torch.randn(B * nblk, page, G, Dv, generator=g)
+    q, gate = torch.randn(B, T, H, D, generator=g) * 0.5, torch.randn(B, T, H * Dv + 8, generator=g)
+    # row 0: make key 2 (kept) and key 40 (out of window for late queries) loud
+    for j in (2, 40):
+        kc[table[0, j // page].long(), j % page] = 2.0
+    q[0, 100:] = 1.0
+    for window, keep in ((37, 3), (64, 0), (0, 0), (200, 5)):
+        want = ref.paged_window_attention(q.bfloat16().float(), kc.bfloat16().float(), vc.bfloat16().float(), table, ctx, ql, 0.2, 25.0, window, keep,
+                                          gate[..., 8:].bfloat16().float())
+        got = ops.paged_window_attention(q.bfloat16().cuda(), kc.bfloat16().cuda(), vc.bfloat16().cuda(), table.cuda(), ctx.int().cuda(), ql.int().cuda(),
+                                         0.2, 25.0, window, keep, gate.bfloat16().cuda()[..., 8:])
+        assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2), (window, keep, float((got.float().cpu() - want).abs().max()))
