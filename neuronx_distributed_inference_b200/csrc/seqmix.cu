@@ -7,6 +7,7 @@
 #include <math.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "seqmix.h"
@@ -283,6 +284,14 @@ __global__ void __launch_bounds__(SPLIT ? 512 : ATT_WARPS * 32) paged_window_att
   float m = -INFINITY, l = 0.f, acc[ATT_VPL];
 #pragma unroll
   for (int i = 0; i < ATT_VPL; ++i) acc[i] = 0.f;
+  // value rows whose byte size is 16 * 2^k (k <= 5) are read as 16-byte pieces, LPR lanes per row
+  constexpr int VN = Vec<T>::N;
+  const int LPR = Dv / VN;
+  const bool vvec = Dv % VN == 0 && LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0;
+  const int sub = vvec ? lane / LPR : 0, piece = vvec ? lane % LPR : 0;
+  float accv[VN];
+#pragma unroll
+  for (int e = 0; e < VN; ++e) accv[e] = 0.f;
   const int nchunks = (n + 31) / 32;
   for (int ch = SPLIT ? warp : 0; ch < nchunks; ch += SPLIT ? nwarps : 1) {
     const int idx = ch * 32 + lane;
@@ -302,16 +311,54 @@ __global__ void __launch_bounds__(SPLIT ? 512 : ATT_WARPS * 32) paged_window_att
     for (int i = 0; i < ATT_VPL; ++i) acc[i] *= corr;
     m = m_new;
     const int cnt = min(32, n - ch * 32);
-    for (int jj = 0; jj < cnt; ++jj) {
-      const float pw = __shfl_sync(0xffffffffu, pj, jj);
-      const long long r = __shfl_sync(0xffffffffu, row, jj);
-      const T* vrow = vc + r * Dv;
+    if (vvec) {
+      // LPR lanes read one value row as 16-byte pieces: 32 / LPR keys per load instruction
 #pragma unroll
-      for (int i = 0; i < ATT_VPL; ++i) {
-        const int dv = lane + 32 * i;
-        if (dv < Dv) acc[i] += pw * ldf(vrow + dv);
+      for (int e = 0; e < VN; ++e) accv[e] *= corr;
+      for (int jj = 0; jj < cnt; jj += 32 / LPR) {
+        const int src = jj + sub;
+        const float pw = __shfl_sync(0xffffffffu, pj, src & 31);
+        const long long r = __shfl_sync(0xffffffffu, row, src & 31);
+        if (src < cnt) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(vc + r * Dv + piece * VN);
+          if constexpr (VN == 4) {
+            accv[0] += pw * __uint_as_float(raw.x); accv[1] += pw * __uint_as_float(raw.y);
+            accv[2] += pw * __uint_as_float(raw.z); accv[3] += pw * __uint_as_float(raw.w);
+          } else {
+            accv[0] += pw * bf16lo(raw.x); accv[1] += pw * bf16hi(raw.x); accv[2] += pw * bf16lo(raw.y); accv[3] += pw * bf16hi(raw.y);
+            accv[4] += pw * bf16lo(raw.z); accv[5] += pw * bf16hi(raw.z); accv[6] += pw * bf16lo(raw.w); accv[7] += pw * bf16hi(raw.w);
+          }
+        }
+      }
+    } else {
+      for (int jj = 0; jj < cnt; ++jj) {
+        const float pw = __shfl_sync(0xffffffffu, pj, jj);
+        const long long r = __shfl_sync(0xffffffffu, row, jj);
+        const T* vrow = vc + r * Dv;
+#pragma unroll
+        for (int i = 0; i < ATT_VPL; ++i) {
+          const int dv = lane + 32 * i;
+          if (dv < Dv) acc[i] += pw * ldf(vrow + dv);
+        }
       }
     }
+  }
+  if (vvec) {
+    // fold the lanes that shared a piece, then hand the row over in the (lane + 32 i) layout the epilogue uses
+    for (int o = LPR; o < 32; o <<= 1)
+#pragma unroll
+      for (int e = 0; e < VN; ++e) accv[e] += __shfl_xor_sync(0xffffffffu, accv[e], o);
+    float* mine = smem + nwarps * D + warp * (Dv + 2);
+    if (sub == 0)
+#pragma unroll
+      for (int e = 0; e < VN; ++e) mine[piece * VN + e] = accv[e];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < ATT_VPL; ++i) {
+      const int dv = lane + 32 * i;
+      acc[i] = dv < Dv ? mine[dv] : 0.f;
+    }
+    __syncwarp();
   }
   if (SPLIT) {
     float* part = smem + nwarps * D + warp * (Dv + 2);
@@ -363,7 +410,7 @@ constexpr int MMA_MT = 64, MMA_KT = 64;
 __device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
 
 template <int D, int DV>
-__global__ void __launch_bounds__(128) paged_window_attention_mma_kernel(WindowAttnParams p) {
+__global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(WindowAttnParams p) {
   constexpr int KS = D + 8, VS = DV + 8, STAGE = MMA_KT * (KS + VS);
   extern __shared__ __align__(16) unsigned char mma_smem[];       // two stages of [64][KS] keys + [64][VS] values
   __nv_bfloat16* stage0 = reinterpret_cast<__nv_bfloat16*>(mma_smem);
@@ -398,6 +445,7 @@ __global__ void __launch_bounds__(128) paged_window_attention_mma_kernel(WindowA
   const __nv_bfloat16* vc = (const __nv_bfloat16*)p.v_cache;
   const int ntA = (nA + MMA_KT - 1) / MMA_KT, ntB = (p_last + 1 - lo + MMA_KT - 1) / MMA_KT, ntiles = ntA + ntB;
   const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const int page_shift = (p.page & (p.page - 1)) == 0 ? __ffs(p.page) - 1 : -1;
   const int warp_pos_lo = ctx + t0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
   // tile i covers keys [j0, min(j0 + 64, end)): first the kept tokens below the window, then the window
   auto tile_range = [&](int i, int& j0, int& end) {
@@ -410,22 +458,22 @@ __global__ void __launch_bounds__(128) paged_window_attention_mma_kernel(WindowA
     tile_range(i, j0, end);
     __nv_bfloat16* Kd = stage0 + (i & 1) * STAGE;
     __nv_bfloat16* Vd = Kd + MMA_KT * KS;
+    // every copy is independent of the others (addresses from the block table, no carried state), so all of them are in flight at
+    // once; pages of 2^k tokens (the usual case) are located with a shift and a mask instead of a division
+    auto copy_rows = [&](const __nv_bfloat16* cache, __nv_bfloat16* dst0, auto Wc, auto LDc) {
+      constexpr int W = decltype(Wc)::value, LD = decltype(LDc)::value, cpr = W / 8;
 #pragma unroll
-    for (int k = 0; k < MMA_KT * (D / 8) / 128; ++k) {
-      const int c = threadIdx.x + 128 * k, r = c / (D / 8), ch = c % (D / 8), j = j0 + r, jj = min(j, end - 1);
-      const long long row = ((long long)table[jj / p.page] * p.page + jj % p.page) * p.G + g;
-      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Kd + r * KS + ch * 8);
-      const int nbytes = j < end ? 16 : 0;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(kc + row * D + ch * 8), "r"(nbytes));
-    }
-#pragma unroll
-    for (int k = 0; k < MMA_KT * (DV / 8) / 128; ++k) {
-      const int c = threadIdx.x + 128 * k, r = c / (DV / 8), ch = c % (DV / 8), j = j0 + r, jj = min(j, end - 1);
-      const long long row = ((long long)table[jj / p.page] * p.page + jj % p.page) * p.G + g;
-      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Vd + r * VS + ch * 8);
-      const int nbytes = j < end ? 16 : 0;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(vc + row * DV + ch * 8), "r"(nbytes));
-    }
+      for (int k = 0; k < MMA_KT * cpr / 128; ++k) {
+        const int c = threadIdx.x + 128 * k, r = c / cpr, ch = c % cpr, j = j0 + r, jj = min(j, end - 1);
+        const int pi = page_shift >= 0 ? (jj >> page_shift) : jj / p.page, po = jj - pi * p.page;
+        const long long row = ((long long)table[pi] * p.page + po) * p.G + g;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(dst0 + r * LD + ch * 8);
+        const int nbytes = j < end ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(cache + row * W + ch * 8), "r"(nbytes));
+      }
+    };
+    copy_rows(kc, Kd, std::integral_constant<int, D>{}, std::integral_constant<int, KS>{});
+    copy_rows(vc, Vd, std::integral_constant<int, DV>{}, std::integral_constant<int, VS>{});
     asm volatile("cp.async.commit_group;");
   };
   load_tile(0);
@@ -693,6 +741,41 @@ __global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ 
   stf(out + i, g * sigmoidf_acc(alpha * g) * (u + 1.f));
 }
 
+// 16 bytes of gate and of up per thread (F a multiple of the vector width)
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F, float limit,
+                                                              float alpha) {
+  constexpr int VN = Vec<T>::N;
+  const int fv = F / VN;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * fv) return;
+  const long long r = i / fv;
+  const int c = (int)(i % fv) * VN;
+  const uint4 gr = *reinterpret_cast<const uint4*>(gu + r * 2 * F + c), ur = *reinterpret_cast<const uint4*>(gu + r * 2 * F + F + c);
+  float g[VN], u[VN], y[VN];
+  if constexpr (VN == 4) {
+    g[0] = __uint_as_float(gr.x); g[1] = __uint_as_float(gr.y); g[2] = __uint_as_float(gr.z); g[3] = __uint_as_float(gr.w);
+    u[0] = __uint_as_float(ur.x); u[1] = __uint_as_float(ur.y); u[2] = __uint_as_float(ur.z); u[3] = __uint_as_float(ur.w);
+  } else {
+    g[0] = bf16lo(gr.x); g[1] = bf16hi(gr.x); g[2] = bf16lo(gr.y); g[3] = bf16hi(gr.y);
+    g[4] = bf16lo(gr.z); g[5] = bf16hi(gr.z); g[6] = bf16lo(gr.w); g[7] = bf16hi(gr.w);
+    u[0] = bf16lo(ur.x); u[1] = bf16hi(ur.x); u[2] = bf16lo(ur.y); u[3] = bf16hi(ur.y);
+    u[4] = bf16lo(ur.z); u[5] = bf16hi(ur.z); u[6] = bf16lo(ur.w); u[7] = bf16hi(ur.w);
+  }
+#pragma unroll
+  for (int e = 0; e < VN; ++e) {
+    const float gg = fminf(g[e], limit), uu = fminf(fmaxf(u[e], -limit), limit);
+    y[e] = gg * sigmoidf_acc(alpha * gg) * (uu + 1.f);
+  }
+  uint4 o;
+  if constexpr (VN == 4) {
+    o = make_uint4(__float_as_uint(y[0]), __float_as_uint(y[1]), __float_as_uint(y[2]), __float_as_uint(y[3]));
+  } else {
+    o = make_uint4(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]), pack_bf16(y[4], y[5]), pack_bf16(y[6], y[7]));
+  }
+  *reinterpret_cast<uint4*>(out + r * F + c) = o;
+}
+
 template <typename K>
 void opt_in_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -771,7 +854,7 @@ void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStrea
   long long span = (long long)p.max_blocks * p.page;
   if (p.window > 0) span = std::min<long long>(span, (long long)p.window + p.keep_first);
   const int nwarps = split ? (int)std::min<long long>(16, std::max<long long>(ATT_WARPS, (span + 63) / 64)) : ATT_WARPS;
-  const size_t smem = sizeof(float) * (size_t)(nwarps * p.D + (split ? nwarps * (p.Dv + 2) : 0));
+  const size_t smem = sizeof(float) * (size_t)(nwarps * (p.D + p.Dv + 2));
   const unsigned grid = (unsigned)(split ? nq : (nq + ATT_WARPS - 1) / ATT_WARPS);
   auto go = [&](auto kernel) {
     opt_in_smem(kernel, smem);
@@ -811,6 +894,15 @@ void group_rmsnorm_launch(const float* y, const float* w, void* out, bool out_lp
 void clamped_glu_launch(const void* gu, void* out, long long rows, int F, float limit, float alpha, bool lp, cudaStream_t st) {
   const long long n = rows * F;
   if (n <= 0) return;
+  const int vn = lp ? 8 : 4;
+  if (F % vn == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const unsigned grid = (unsigned)((n / vn + 255) / 256);
+    if (lp)
+      clamped_glu_vec_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F, limit, alpha);
+    else
+      clamped_glu_vec_kernel<float><<<grid, 256, 0, st>>>((const float*)gu, (float*)out, rows, F, limit, alpha);
+    return;
+  }
   const unsigned grid = (unsigned)((n + 255) / 256);
   if (lp)
     clamped_glu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F, limit, alpha);

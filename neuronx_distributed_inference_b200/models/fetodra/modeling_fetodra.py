@@ -57,7 +57,8 @@ class FetodraInferenceConfig(InferenceConfig):
                 m, s = layer["mixer"], self.layers[src]["mixer"]
                 if self.layers[src]["type"] != "attention" or s.get("kv_from") is not None or src >= i:
                     raise ValueError(f"layer {i}: kv_from must name an earlier attention layer with keys of its own")
-                if (m["kv_heads"], m["dim"], m["vdim"]) != (s["kv_heads"], s["dim"], s["vdim"]):
+                shape = lambda x: (x.get("kv_heads", x["heads"]), x["dim"], x.get("vdim", x["dim"]))      # noqa: E731
+                if shape(m) != shape(s):
                     raise ValueError(f"layer {i}: key / value shape differs from layer {src}")
 
     @classmethod
@@ -99,14 +100,16 @@ class NeuronFetodraModel(NeuronBaseModel):
         for i, spec in enumerate(config.layers):
             m = spec["mixer"]
             if spec["type"] == "attention":
-                mask = m.get("mask") or {}
-                mixer = ConvWindowAttention(W, m["heads"], m["kv_heads"], m["dim"], m["vdim"], conv_taps=m["conv"],
-                                            rot_dims=m["rot"]["dims"], rot_base=float(m["rot"]["base"]), scale=float(m["scale"]),
+                mask, rot = m.get("mask") or {}, m.get("rot") or {}
+                mixer = ConvWindowAttention(W, m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"]),
+                                            conv_taps=int(m.get("conv") or 1), rot_dims=int(rot.get("dims") or 0),
+                                            rot_base=float(rot.get("base") or 10000.0),
+                                            scale=float(m["scale"]) if m.get("scale") is not None else m["dim"] ** -0.5,
                                             softcap=m.get("softcap"), window=mask.get("size"), keep_first=int(mask.get("keep_first") or 0),
                                             eps=eps, layer_idx=i, kv_source=m.get("kv_from"), dtype=dt, device=dev, tp_group=self.tp_group)
             else:
-                mixer = RaggedMamba2Mixer(W, m["heads"], m["vdim"], m["state"], m["groups"], m["norm_groups"], m["conv"], eps, i,
-                                          dtype=dt, device=dev, tp_group=self.tp_group)
+                mixer = RaggedMamba2Mixer(W, m["heads"], m["vdim"], m["state"], int(m.get("groups") or 1), int(m.get("norm_groups") or 1),
+                                          int(m.get("conv") or 1), eps, i, dtype=dt, device=dev, tp_group=self.tp_group)
             f = spec.get("mlp")
             mlp = ClampedGLUMLP(W, f["ff"], f["limit"], GLU_ALPHA, dt, self.tp_group, dev) if f is not None else None
             layers.append(PostNormDecoderLayer(mixer, mlp, norm(), norm() if f is not None else None, config.postln_alpha, i))
@@ -188,8 +191,10 @@ class NeuronFetodraForCausalLM(NeuronBaseForCausalLM):
                 names = ["q", "k", "v"] if own else ["q"]
                 g = sd[x + "g"]
                 out[y + "in_proj.weight"] = torch.cat([sd[x + n] for n in names] + [g], 0)
-                out[y + "in_proj.bias"] = torch.cat([sd[x + n + ".b"] for n in names] + [torch.zeros(g.shape[0], dtype=g.dtype)], 0)
-                out[y + "conv_weight"] = torch.cat([sd[x + n + ".conv"] for n in names], 0)
+                zeros = lambda n: torch.zeros(sd[x + n].shape[0], dtype=g.dtype)                               # noqa: E731
+                ident = lambda n: torch.ones(sd[x + n].shape[0], 1, dtype=g.dtype)                               # noqa: E731
+                out[y + "in_proj.bias"] = torch.cat([sd.get(x + n + ".b", zeros(n)) for n in names] + [torch.zeros(g.shape[0], dtype=g.dtype)], 0)
+                out[y + "conv_weight"] = torch.cat([sd.get(x + n + ".conv", ident(n)) for n in names], 0)
                 out[y + "q_norm_weight"] = sd[x + "q.norm"]
                 if own:
                     out[y + "k_norm_weight"] = sd[x + "k.norm"]
@@ -197,7 +202,12 @@ class NeuronFetodraForCausalLM(NeuronBaseForCausalLM):
             else:
                 for src, dst in (("in", "in_proj.weight"), ("conv", "conv_weight"), ("conv.b", "conv_bias"), ("dt_bias", "dt_bias"),
                                  ("A_log", "A_log"), ("D", "D"), ("norm", "norm_weight"), ("o", "out_proj.weight")):
-                    out[y + dst] = sd[x + src]
+                    if x + src in sd:
+                        out[y + dst] = sd[x + src]
+                if x + "conv" not in sd:                                 # a stack without the short convolution: one tap of weight one
+                    m = spec["mixer"]
+                    cd = m["heads"] * m["vdim"] + 2 * int(m.get("groups") or 1) * m["state"]
+                    out[y + "conv_weight"] = torch.ones(cd, 1, dtype=sd[x + "in"].dtype)
             if spec.get("mlp") is not None:
                 out[b + "norm2.weight"] = sd[a + "norm2"]
                 out[b + "mlp.gate_up_proj.weight"] = torch.cat([sd[a + "mlp.gate"], sd[a + "mlp.up"]], 0)

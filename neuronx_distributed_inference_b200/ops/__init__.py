@@ -427,6 +427,8 @@ quantize_blockwise = ref.quantize_blockwise
 
 # ---- sequence mixers on ragged rows (csrc/seqmix.cu; definitions and conventions in ops/reference.py) ---------------------------
 _MIX_DTYPES = (torch.bfloat16, torch.float32)
+# launch limits of csrc/seqmix.cu (seqmix.h); shapes beyond them run the PyTorch definitions on the same device
+_MIX_MAX_TAPS, _MIX_MAX_VDIM, _MIX_MAX_STATE = 8, 256, 256
 
 
 def _mix_cuda(x) -> bool:
@@ -449,14 +451,14 @@ def scaled_add_rmsnorm(x, y, weight, alpha: float, eps: float, offset: float = 0
 
 
 def short_conv(u, weight, bias, state, slots, ctx_len, q_len, silu: bool = False):
-    if _mix_cuda(u) and u.stride(-1) == 1:
+    if _mix_cuda(u) and u.stride(-1) == 1 and weight.shape[1] <= _MIX_MAX_TAPS:
         stats["short_conv"] += 1
         return _C().short_conv(u, weight, bias, state, _i32(slots), _i32(ctx_len), _i32(q_len), bool(silu))
     return ref.short_conv(u, weight, bias, state, slots, ctx_len, q_len, silu)
 
 
 def short_conv_update(u, state, slots, ctx_len, q_len):
-    if _mix_cuda(u) and u.stride(-1) == 1:
+    if _mix_cuda(u) and u.stride(-1) == 1 and state.shape[1] < _MIX_MAX_TAPS:
         stats["short_conv_update"] += 1
         return _C().short_conv_update(u, state, _i32(slots), _i32(ctx_len), _i32(q_len))
     return ref.short_conv_update(u, state, slots, ctx_len, q_len)
@@ -464,7 +466,7 @@ def short_conv_update(u, state, slots, ctx_len, q_len):
 
 def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w, k_norm_w, eps, n_q, n_kv, D, Dv, cos, sin,
                             k_cache, v_cache, block_table, out_dtype=None):
-    if _mix_cuda(qkv) and qkv.stride(-1) == 1:
+    if _mix_cuda(qkv) and qkv.stride(-1) == 1 and conv_w.shape[1] <= _MIX_MAX_TAPS and D % 2 == 0:
         stats["conv_qknorm_rope_append"] += 1
         return _C().conv_qknorm_rope_append(qkv, conv_w, state, _i32(slots), _i32(ctx_len), _i32(q_len), q_norm_w, k_norm_w, float(eps),
                                             int(n_q), int(n_kv), int(D), int(Dv), cos.float().contiguous(), sin.float().contiguous(),
@@ -474,7 +476,7 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
 
 
 def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate=None):
-    if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1):
+    if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1) and v_cache.shape[-1] <= _MIX_MAX_VDIM:
         stats["paged_window_attention"] += 1
         return _C().paged_window_attention(q.contiguous(), k_cache, v_cache, _i32(block_table), _i32(ctx_len), _i32(q_len), float(scale),
                                            float(softcap or 0.0), int(window or 0), int(keep_first or 0), gate)
@@ -482,7 +484,8 @@ def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, sca
 
 
 def ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads, head_dim, n_state, n_groups):
-    if _use_cuda(xBC) and xBC.dtype == torch.float32 and dt_raw.dtype in _MIX_DTYPES and state.dtype == torch.float32:
+    if (_use_cuda(xBC) and xBC.dtype == torch.float32 and dt_raw.dtype in _MIX_DTYPES and state.dtype == torch.float32
+            and n_state <= _MIX_MAX_STATE):
         stats["ssd_scan"] += 1
         return _C().ssd_scan(xBC.contiguous(), dt_raw, z, A_log, dt_bias, D_skip, state, _i32(slots), _i32(ctx_len), _i32(q_len),
                              int(n_heads), int(head_dim), int(n_state), int(n_groups))

@@ -95,6 +95,14 @@ class PagedBatchEngine:
         ``[len(want), vocab]`` per entry (CPU), or with ``sample`` the token sampled after each entry's LAST token."""
         if not entries:
             return []
+        if any(len(toks) == 0 for _, toks, _ in entries):
+            # an entry without tokens takes no part in the forward (its request stays admitted)
+            full = [e for e in entries if len(e[1])]
+            done = iter(self.step(full, sample))
+            for rid, toks, _ in entries:
+                if not len(toks):
+                    self.admit(rid)
+            return [next(done) if len(toks) else (None if sample else torch.zeros(0, 0)) for _, toks, _ in entries]
         if len(entries) > self.max_rows:
             raise ValueError(f"{len(entries)} rows in one step; the engine was sized for {self.max_rows}")
         seqs = [self.admit(rid) for rid, _, _ in entries]

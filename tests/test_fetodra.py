@@ -409,3 +409,24 @@ def test_gpu_tensor_core_attention_on_prompt_portions(D, Dv):
         got = ops.paged_window_attention(q.bfloat16().cuda(), kc.bfloat16().cuda(), vc.bfloat16().cuda(), table.cuda(), ctx.int().cuda(), ql.int().cuda(),
                                          0.2, 25.0, window, keep, gate.bfloat16().cuda()[..., 8:])
         assert torch.allclose(got.float().cpu(), want, atol=2e-2, rtol=2e-2), (window, keep, float((got.float().cpu() - want).abs().max()))
+
+
+def test_command_line_generates_from_token_ids(tmp_path, capsys):
+    """``inference_demo --model-type fetodra ... --prompt-token-ids`` runs the engine's scheduler and prints the generated ids."""
+    from neuronx_distributed_inference_b200 import inference_demo
+    cfg = make_config(HYBRID)
+    w = make_weights(cfg)
+    eng = make_engine(tmp_path, cfg, w)
+    want = eng.generate([[1, 2, 3, 4], [7, 8]], 5)
+    inference_demo.main(["--model-type", "fetodra", "--task-type", "causal-lm", "run", "--model-path", str(tmp_path / "ckpt"),
+                         "--compiled-model-path", str(tmp_path / "c"), "--on-cpu", "--torch-dtype", "float32", "--prompt-token-ids", "1,2,3,4",
+                         "--prompt-token-ids", "7,8", "--max-new-tokens", "5", "--pa-block-size", str(PAGE)])
+    out = capsys.readouterr().out
+    assert "Output 0: " + ",".join(map(str, want[0])) in out and "Output 1: " + ",".join(map(str, want[1])) in out
+
+
+def test_step_accepts_an_entry_without_tokens(tmp_path):
+    cfg = make_config(HYBRID[:2])
+    eng = make_engine(tmp_path, cfg, make_weights(cfg))
+    rows = eng.step([("a", [1, 2, 3], [2]), ("b", [], [])])
+    assert rows[0].shape == (1, cfg["vocab"]) and rows[1].shape[0] == 0 and "b" in eng.live
