@@ -256,7 +256,7 @@ constexpr int ATT_VPL = SEQMIX_MAX_VDIM / 32;      // value channels per lane
 // SPLIT = false: warp w of a block owns query blockIdx.x * 4 + w.  SPLIT = true: the four warps share query blockIdx.x, warp w takes
 // key chunks w, w + 4, ... and the partial (max, sum, acc) are merged through shared memory (few queries, long ranges: decode).
 template <typename T, bool SPLIT>
-__global__ void __launch_bounds__(SPLIT ? 512 : ATT_WARPS * 32) paged_window_attention_kernel(WindowAttnParams p) {
+__global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_attention_kernel(WindowAttnParams p) {
   extern __shared__ float smem[];      // [warps][D] scaled queries, then (SPLIT) [warps][Dv + 2] partials
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const long long nq = (long long)p.B * p.T * p.Hq;
@@ -676,7 +676,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, NB == 1 ? 4 : 2) ssd_scan_kernel
     }
     __syncthreads();
     if (t0 + SCAN_TT < n_tok) fetch(t0 + SCAN_TT);      // in flight while this round computes
-    for (int t = 0; t < tt; ++t) {
+#pragma unroll 4
+    for (int t = 0; t < tt; ++t) {       // unrolled: the lane reduction of step t overlaps the state update of step t + 1
       const float dA = dAs[t], dx = dts[t] * xs[t * SCAN_PT + pl];
       const float4* Bt = reinterpret_cast<const float4*>(Bs + t * NP) + ns * (NPT * 5 / 16);
       const float4* Ct = reinterpret_cast<const float4*>(Cs + t * NP) + ns * (NPT * 5 / 16);
@@ -850,10 +851,10 @@ void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStrea
   }
   // few queries (decode steps): one block per query, its warps split the keys; otherwise one warp per query
   const bool split = nq <= 2LL * kNumSMs * 4;
-  // split mode: one warp per 64 visible keys (bounded by the window or by the pages a row can hold), 4 to 16 warps
+  // split mode: one warp per 32 visible keys (bounded by the window or by the pages a row can hold), 4 to 32 warps
   long long span = (long long)p.max_blocks * p.page;
   if (p.window > 0) span = std::min<long long>(span, (long long)p.window + p.keep_first);
-  const int nwarps = split ? (int)std::min<long long>(16, std::max<long long>(ATT_WARPS, (span + 63) / 64)) : ATT_WARPS;
+  const int nwarps = split ? (int)std::min<long long>(32, std::max<long long>(ATT_WARPS, (span + 31) / 32)) : ATT_WARPS;
   const size_t smem = sizeof(float) * (size_t)(nwarps * (p.D + p.Dv + 2));
   const unsigned grid = (unsigned)(split ? nq : (nq + ATT_WARPS - 1) / ATT_WARPS);
   auto go = [&](auto kernel) {

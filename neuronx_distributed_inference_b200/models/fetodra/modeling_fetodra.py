@@ -77,8 +77,15 @@ class FetodraInferenceConfig(InferenceConfig):
 
 
 class NeuronFetodraModel(NeuronBaseModel):
-    graph_safe = False
     meta_extra_keys = ("computed_context_lens",)
+    # decode steps (one token per row) replay from a CUDA graph: these per-step tensors are staged into the graph's static inputs
+    graph_tensor_kwargs = ("slot_mapping", "block_table", "computed_context_lens", "gather_positions")
+
+    def __init__(self, config, device=None):
+        super().__init__(config, device)
+        # every op of a step is a sync-free kernel launch or a torch op on static shapes; rows with seq_id -1 (graph warm-up, batch
+        # padding) have q_len 0 and touch neither cache nor state
+        self.graph_safe = device is not None and torch.device(device).type == "cuda"
 
     def setup_attr_for_model(self, config):
         nc = config.neuron_config

@@ -38,8 +38,8 @@ def ragged_rope_tables(meta, T: int, rot_dims: int, rot_base: float):
     if key not in meta.extras:
         ctx = meta.extras["ctx_len"]
         pos = ctx.double().view(-1, 1) + torch.arange(T, device=ctx.device, dtype=torch.float64).view(1, T)
-        inv = torch.tensor(float(rot_base), dtype=torch.float64, device=ctx.device) ** (
-            -torch.arange(0, rot_dims, 2, device=ctx.device, dtype=torch.float64) / rot_dims)
+        # (scalar ** tensor: no host-to-device copy, so the step stays capturable in a CUDA graph)
+        inv = float(rot_base) ** (-torch.arange(0, rot_dims, 2, device=ctx.device, dtype=torch.float64) / rot_dims)
         ang = pos.unsqueeze(-1) * inv
         meta.extras[key] = (torch.cos(ang).float().contiguous(), torch.sin(ang).float().contiguous())
     return meta.extras[key]

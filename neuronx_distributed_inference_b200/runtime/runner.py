@@ -344,7 +344,11 @@ class SubModelRunner:
         dev = self.device
         B, T = input_ids.shape
         kwargs = self._common_kwargs(kw)
-        graphable = self.use_graphs and not any(torch.is_tensor(v) for v in kwargs.values())
+        # tensor arguments that a model lists in ``graph_tensor_kwargs`` (leading dim = batch, fixed trailing shape per graph: block
+        # table, slot mapping, context lengths ...) are staged into static buffers like the ids; any other tensor argument means eager
+        static_names = tuple(getattr(self.model, "graph_tensor_kwargs", ()))
+        tensor_kw = {k: v for k, v in kwargs.items() if torch.is_tensor(v)}
+        graphable = self.use_graphs and all(k in static_names and v.shape[:1] == (B,) for k, v in tensor_kw.items())
         if not graphable:
             self.n_launch += 1
             with torch.no_grad():
@@ -357,7 +361,8 @@ class SubModelRunner:
         else:
             cur = self.seq_buckets[-1] - 1  # device-resident inputs: no sync, take the largest bucket
         sb = self.get_target_bucket(cur)
-        key = (Bb, sb, T, tuple(sorted((k, v) for k, v in kwargs.items() if not torch.is_tensor(v))))
+        key = (Bb, sb, T, tuple(sorted((k, v) for k, v in kwargs.items() if not torch.is_tensor(v))),
+               tuple(sorted((k, tuple(v.shape[1:]), v.dtype) for k, v in tensor_kw.items())))
         g = self._graphs.get(key)
         if g is None:
             try:
@@ -378,6 +383,8 @@ class SubModelRunner:
             si["position_ids"][B:].fill_(0)
         if sampling_params is not None:
             si["sampling_params"][:B].copy_(sampling_params, non_blocking=True)
+        for k, v in tensor_kw.items():
+            si["kw:" + k][:B].copy_(v, non_blocking=True)
         self._symm_even()
         g.graph.replay()
         self.n_launch += 1
@@ -396,6 +403,11 @@ class SubModelRunner:
             sampling_params=torch.tensor([[1.0, 1.0, 1.0]], device=dev).repeat(Bb, 1),
         )
         si = g.inputs
+        kwargs = dict(kwargs)
+        for k, v in list(kwargs.items()):
+            if torch.is_tensor(v):       # static copy with the graph's batch rows; rows past the live batch belong to seq_id -1
+                si["kw:" + k] = torch.zeros((Bb,) + tuple(v.shape[1:]), dtype=v.dtype, device=dev)
+                kwargs[k] = si["kw:" + k]
 
         def step():
             # seq_hint: the graph of sequence bucket `sb` bakes a split-KV grid sized for sb keys, not for the whole cache

@@ -116,6 +116,7 @@ class PagedBatchEngine:
             self._reserve(seq, len(toks))
         K = 1 if sample else max(1, max(len(w) for _, _, w in entries))
         P = max(len(s.pages) for s in seqs)
+        P = 1 << (P - 1).bit_length()                    # block-table width in powers of two: few distinct decode graphs
         ids = torch.zeros(B, T, dtype=torch.long)
         mask = torch.zeros(B, T, dtype=torch.int32)
         pos = torch.zeros(B, T, dtype=torch.int32)
