@@ -590,14 +590,14 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
 
 // ---- Mamba-2 recurrence with a carried state ----------------------------------------------------------------------------------
 // Block = one (row, head, 16 head channels); 8 lanes split the state axis of a channel and hold their share of S in registers.  Time
-// runs in rounds of 16 steps: the B / C / x / dt / z values of round r + 1 are fetched into registers while round r is computed out
-// of shared memory, so the global-load latency is paid once per sequence instead of once per round.
+// runs in batches of 16 steps: the B / C / x / dt / z values of batch r + 1 are fetched into registers while batch r is computed out
+// of shared memory, so the global-load latency is paid once per sequence instead of once per batch.
 constexpr int SCAN_PT = 16;      // head channels per block
 constexpr int SCAN_NS = 8;       // lanes that split the state axis for one channel
-constexpr int SCAN_TT = 16;      // time steps staged per round
+constexpr int SCAN_TT = 16;      // time steps staged per batch
 constexpr int SCAN_THREADS = SCAN_PT * SCAN_NS;
 
-// NB = ceil(N / 128): state values per lane = 16 * NB, staged B / C values per thread and round = 16 * NB
+// NB = ceil(N / 128): state values per lane = 16 * NB, staged B / C values per thread and batch = 16 * NB
 template <typename T, int NB>
 __global__ void __launch_bounds__(SCAN_THREADS, NB == 1 ? 4 : 2) ssd_scan_kernel(SsdScanParams p) {
   extern __shared__ float sm[];
@@ -657,7 +657,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, NB == 1 ? 4 : 2) ssd_scan_kernel
   fetch(0);
   for (int t0 = 0; t0 < n_tok; t0 += SCAN_TT) {
     const int tt = min(SCAN_TT, n_tok - t0);
-    __syncthreads();                      // the previous round's readers are done with the tiles
+    __syncthreads();                      // the readers of the previous batch are done with the tiles
 #pragma unroll
     for (int t = 0; t < SCAN_TT; ++t)
 #pragma unroll
@@ -675,7 +675,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, NB == 1 ? 4 : 2) ssd_scan_kernel
       dAs[tid] = expf(negA * dt);
     }
     __syncthreads();
-    if (t0 + SCAN_TT < n_tok) fetch(t0 + SCAN_TT);      // in flight while this round computes
+    if (t0 + SCAN_TT < n_tok) fetch(t0 + SCAN_TT);      // in flight while the current steps are computed
 #pragma unroll 4
     for (int t = 0; t < tt; ++t) {       // unrolled: the lane reduction of step t overlaps the state update of step t + 1
       const float dA = dAs[t], dx = dts[t] * xs[t * SCAN_PT + pl];

@@ -19,6 +19,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Tuple
 from typing import Sequence as Seq
 
+import numpy as np
 import torch
 
 
@@ -69,6 +70,26 @@ class PagedBatchEngine:
         self.max_rows = min(nc.ctx_batch_size, nc.tkg_batch_size)
         self.max_row_tokens = nc.max_context_length
         self.live: Dict[object, Sequence] = {}
+        self.device = torch.device(app.device) if app.device is not None else torch.device("cpu")
+        self._host = None
+        self._sp: Dict[int, torch.Tensor] = {}
+
+    def _staging(self, n: int) -> torch.Tensor:
+        """Reusable int32 host buffer of ``n`` elements; safe to refill every step because a step ends by reading its result back."""
+        if self._host is None or self._host.numel() < n:
+            self._host = torch.empty(max(n, 4096), dtype=torch.int32)
+            if self.device.type == "cuda":
+                self._host = self._host.pin_memory()
+        return self._host[:n]
+
+    def _sampling_rows(self, B: int) -> torch.Tensor:
+        """The configured sampling parameters for ``B`` rows, resident on the engine's device."""
+        if B not in self._sp:
+            from ..modules.sampling import prepare_sampling_params
+            c = self.app.neuron_config.on_device_sampling_config
+            sp = prepare_sampling_params(B, c.top_k, c.top_p, c.temperature) if c is not None else prepare_sampling_params(B)
+            self._sp[B] = sp.to(self.device)
+        return self._sp[B]
 
     # ---- requests ----------------------------------------------------------------------------------------------------
     def admit(self, rid) -> Sequence:
@@ -117,29 +138,36 @@ class PagedBatchEngine:
         K = 1 if sample else max(1, max(len(w) for _, _, w in entries))
         P = max(len(s.pages) for s in seqs)
         P = 1 << (P - 1).bit_length()                    # block-table width in powers of two: few distinct decode graphs
-        ids = torch.zeros(B, T, dtype=torch.long)
-        mask = torch.zeros(B, T, dtype=torch.int32)
-        pos = torch.zeros(B, T, dtype=torch.int32)
-        slot_map = torch.full((B, T), -1, dtype=torch.int32)
-        table = torch.zeros(B, P, dtype=torch.int32)
-        ctx = torch.zeros(B, dtype=torch.int32)
-        gather = torch.zeros(B, K, dtype=torch.int32)
+        # every integer input of the step is laid out in ONE staging buffer (pinned on a GPU engine) and reaches the device in one copy:
+        # ids | mask | positions | slot mapping (each [B, T]) | block table [B, P] | wanted indices [B, K] | state slots [B]
+        sizes = [B * T] * 4 + [B * P, B * K, B]
+        offs = np.cumsum([0] + sizes)
+        host = self._staging(int(offs[-1]))
+        flat = host.numpy()
+        flat[:] = 0
+        ids, mask, pos, slot_map = (flat[offs[i]:offs[i + 1]].reshape(B, T) for i in range(4))
+        table, gather, slots = flat[offs[4]:offs[5]].reshape(B, P), flat[offs[5]:offs[6]].reshape(B, K), flat[offs[6]:offs[7]]
+        slot_map[:] = -1
+        ctx = np.zeros(B, dtype=np.int32)
         for b, (seq, (_, toks, want)) in enumerate(zip(seqs, entries)):
             n = len(toks)
-            ids[b, :n] = torch.as_tensor(list(toks), dtype=torch.long)
+            ids[b, :n] = np.asarray(toks, dtype=np.int32)
             mask[b, :n] = 1
-            p = torch.arange(seq.length, seq.length + n, dtype=torch.int32)
+            p = np.arange(seq.length, seq.length + n, dtype=np.int32)
             pos[b, :n] = p
-            pg = torch.as_tensor(seq.pages, dtype=torch.int32)
-            table[b, :len(seq.pages)] = pg
-            slot_map[b, :n] = pg[(p // self.page).long()] * self.page + p % self.page
+            pg = np.asarray(seq.pages, dtype=np.int32)
+            table[b, :len(pg)] = pg
+            slot_map[b, :n] = pg[p // self.page] * self.page + p % self.page
             ctx[b] = seq.length
+            slots[b] = seq.slot
             w = [n - 1] if sample else list(want)
             if w:
-                gather[b, :len(w)] = torch.as_tensor(w, dtype=torch.int32)
-        out = self.app(ids, attention_mask=mask, position_ids=pos, seq_ids=torch.as_tensor([s.slot for s in seqs], dtype=torch.int32),
-                       slot_mapping=slot_map, block_table=table, computed_context_lens=ctx, gather_positions=gather,
-                       output_logits=not sample)
+                gather[b, :len(w)] = np.asarray(w, dtype=np.int32)
+        dev = host.to(self.device, non_blocking=True) if self.device.type == "cuda" else host.clone()
+        part = lambda i, *shape: dev[int(offs[i]):int(offs[i + 1])].view(*shape)          # noqa: E731
+        out = self.app(part(0, B, T), attention_mask=part(1, B, T), position_ids=part(2, B, T), seq_ids=part(6, B),
+                       sampling_params=self._sampling_rows(B), slot_mapping=part(3, B, T), block_table=part(4, B, P),
+                       computed_context_lens=torch.from_numpy(ctx), gather_positions=part(5, B, K), output_logits=not sample)
         for seq, (_, toks, _) in zip(seqs, entries):
             seq.length += len(toks)
         if sample:
