@@ -234,7 +234,7 @@ def test_rotation_pairs_and_partial_width():
     assert torch.allclose(got, want.float(), atol=1e-6) and torch.equal(got[..., 4:], x[..., 4:].float())
 
 
-def window_case(dev, dtype, target, pos, window, keep, page=4):
+def window_case(dev, dtype, target, pos, window, keep, page=4, as_prompt=False):
     """One query at ``pos`` whose key at ``target`` is made to dominate: returns (op output, plain output)."""
     from neuronx_distributed_inference_b200 import ops
     H, G, D, Dv = 2, 1, 8, 4
@@ -250,19 +250,42 @@ def window_case(dev, dtype, target, pos, window, keep, page=4):
     for j in range(n):
         kc[perm[j // page], j % page], vc[perm[j // page], j % page] = k[j], v[j]
     to = lambda t: t.to(dev, dtype)                                      # noqa: E731
-    got = ops.paged_window_attention(to(q[pos].view(1, 1, H, D)), to(kc), to(vc), perm.view(1, -1).int().to(dev), torch.tensor([pos]).int().to(dev),
-                                     torch.tensor([1]).int().to(dev), 0.25, 40.0, window, keep)
+    if as_prompt:        # all positions 0 .. pos in one portion; the last row is the query under test
+        got = ops.paged_window_attention(to(q.view(1, n, H, D)), to(kc), to(vc), perm.view(1, -1).int().to(dev), torch.tensor([0]).int().to(dev),
+                                         torch.tensor([n]).int().to(dev), 0.25, 40.0, window, keep)[0, -1]
+    else:                # decoded alone against the cache
+        got = ops.paged_window_attention(to(q[pos].view(1, 1, H, D)), to(kc), to(vc), perm.view(1, -1).int().to(dev),
+                                         torch.tensor([pos]).int().to(dev), torch.tensor([1]).int().to(dev), 0.25, 40.0, window, keep)
     return got.float().cpu().view(-1), want.float()
 
 
 @pytest.mark.parametrize("target,pos,visible", [(0, 90, True), (2, 90, True), (3, 90, False), (90 - 11, 90, True), (90 - 12, 90, False),
                                                 (40, 90, False), (15, 16, True), (4, 15, True), (3, 15, False), (7, 8, True)])
-def test_window_edges_kept_tokens_and_page_borders(target, pos, visible):
-    got, want = window_case("cpu", torch.float32, target, pos, window=12, keep=3)
+@pytest.mark.parametrize("as_prompt", [False, True])
+def test_window_edges_kept_tokens_and_page_borders(target, pos, visible, as_prompt):
+    got, want = window_case("cpu", torch.float32, target, pos, window=12, keep=3, as_prompt=as_prompt)
     assert torch.allclose(got, want, atol=1e-5)
     # the dominant key decides the output exactly when it is visible
-    got_far, _ = window_case("cpu", torch.float32, target, pos, window=10 ** 6, keep=0)
+    got_far, _ = window_case("cpu", torch.float32, target, pos, window=10 ** 6, keep=0, as_prompt=as_prompt)
     assert (torch.allclose(got, got_far, atol=1e-3)) == visible
+
+
+def test_norms_and_gate_product_match_the_plain_functions():
+    from neuronx_distributed_inference_b200 import ops
+    g = torch.Generator().manual_seed(8)
+    x, y, wn = torch.randn(5, 24, generator=g), torch.randn(5, 24, generator=g), torch.randn(24, generator=g) * 0.2
+    out, lp = ops.scaled_add_rmsnorm(x, y, wn, 1.7, 1e-3, 1.0, torch.bfloat16)
+    want = oracle.offset_rms_norm(1.7 * x.double() + y.double(), wn.double(), 1e-3)
+    assert torch.allclose(out.double(), want, atol=1e-5) and lp.dtype == torch.bfloat16 and torch.allclose(lp.double(), want, atol=2e-2)
+    yv, wg = torch.randn(5, 24, generator=g), torch.randn(24, generator=g)
+    want = oracle.rms_unit(yv.double().view(5, 3, 8), 1e-3).reshape(5, 24) * wg.double()
+    assert torch.allclose(ops.group_rmsnorm(yv, wg, 3, 1e-3).double(), want, atol=1e-5)
+    W, F = 6, 10
+    h, wt = torch.randn(4, W, generator=g).double() * 2, {"gate": torch.randn(F, W, generator=g).double(), "up": torch.randn(F, W, generator=g).double(),
+                                                         "down": torch.eye(F).double()}
+    gu = torch.cat([h @ wt["gate"].T, h @ wt["up"].T], -1)
+    assert (gu.abs() > 0.9).any()                                        # both clamps bite
+    assert torch.allclose(ops.clamped_glu(gu.float(), 0.9, 1.702).double(), oracle.clamped_glu(h, wt, "", dict(limit=0.9)), atol=1e-5)
 
 
 def test_scan_state_carries_across_portions_and_reused_lines():
@@ -322,6 +345,8 @@ def test_gpu_hybrid_stack_schedules_mixed_batches_and_generation(tmp_path, dtype
     for k in ("scaled_add_rmsnorm", "short_conv", "short_conv_update", "conv_qknorm_rope_append", "paged_window_attention", "ssd_scan",
               "group_rmsnorm", "clamped_glu"):
         assert ops.stats[k] > 0, k
+    tkg = eng.app.token_generation_model          # single-token steps replayed from CUDA graphs (capture did not fall back to eager)
+    assert tkg.use_graphs and len(tkg._graphs) > 0
 
 
 @pytest.mark.gpu
