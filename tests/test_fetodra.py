@@ -353,11 +353,11 @@ def test_gpu_hybrid_stack_schedules_mixed_batches_and_generation(tmp_path, dtype
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_gpu_wider_stack(tmp_path, dtype):
     """Head sizes with 16-byte rows (vector loads), more heads than a warp's value lanes need, several norm groups."""
-    layers = [layer("attention", attn(heads=8, kv_heads=2, dim=64, vdim=96, conv=3, rot=32, window=20, keep=4, softcap=30.0, scale=0.1), ff=256),
+    layers = [layer("attention", attn(heads=6, kv_heads=2, dim=64, vdim=96, conv=4, rot=16, window=20, keep=4, softcap=20.0, scale=0.1), ff=320),
               layer("mamba2", mamba(heads=8, vdim=40, state=48, groups=2, norm_groups=4, conv=4), ff=None),
-              layer("attention", attn(heads=8, kv_heads=2, dim=64, vdim=96, conv=3, rot=32, window=20, keep=4, softcap=30.0, scale=0.1, kv_from=0),
-                    ff=256)]
-    eng, cfg, w = check_schedules(tmp_path, "cuda", dtype, layers=layers, T=77, width=256, vocab=301, alpha=2.0, eps=1e-5, seed=7)
+              layer("attention", attn(heads=6, kv_heads=2, dim=64, vdim=96, conv=4, rot=16, window=20, keep=4, softcap=20.0, scale=0.1, kv_from=0),
+                    ff=320)]
+    eng, cfg, w = check_schedules(tmp_path, "cuda", dtype, layers=layers, T=77, width=256, vocab=301, alpha=1.25, eps=1e-6, seed=7)
     check_mixed_batches(eng, cfg, w, dtype, n_req=5)
 
 
