@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const T* __restrict__ u
                                                          const T* __restrict__ state, const int* __restrict__ lines,
                                                          const int* __restrict__ ctx_len, const int* __restrict__ q_len,
                                                          float* __restrict__ y, int T_, int C, int K, int silu) {
-  const int b = blockIdx.z, t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.z, t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;      // tokens on grid.x: no 65535 limit
   if (c >= C || t >= q_len[b]) return;
   const bool has_ctx = ctx_len[b] > 0;
   const T* u0 = u + (long long)b * u_sb;
@@ -718,7 +718,7 @@ template <typename TO>
 __global__ void __launch_bounds__(256) group_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ w, TO* __restrict__ out,
                                                             int W, int gw, float eps) {
   __shared__ float red[32];
-  const long long base = (long long)blockIdx.y * W + (long long)blockIdx.x * gw;
+  const long long base = (long long)blockIdx.x * W + (long long)blockIdx.y * gw;      // rows on grid.x: no 65535 limit
   float ss = 0.f;
   for (int c = threadIdx.x; c < gw; c += blockDim.x) {
     const float v = y[base + c];
@@ -726,7 +726,7 @@ __global__ void __launch_bounds__(256) group_rmsnorm_kernel(const float* __restr
   }
   ss = block_sum(ss, red);
   const float r = 1.f / sqrtf(ss / (float)gw + eps);
-  for (int c = threadIdx.x; c < gw; c += blockDim.x) stf(out + base + c, y[base + c] * r * w[blockIdx.x * gw + c]);
+  for (int c = threadIdx.x; c < gw; c += blockDim.x) stf(out + base + c, y[base + c] * r * w[blockIdx.y * gw + c]);
 }
 
 // ---- clamped gate product -----------------------------------------------------------------------------------------------------
@@ -797,7 +797,7 @@ void short_conv_launch(const void* u, long long u_sb, long long u_st, const floa
                        const int* lines, const int* ctx_len, const int* q_len, float* y, int B, int T, int C, int K, bool silu, bool lp,
                        cudaStream_t st) {
   if (B <= 0 || T <= 0) return;
-  dim3 grid((C + 255) / 256, T, B);
+  dim3 grid(T, (C + 255) / 256, B);
   if (lp)
     short_conv_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)u, u_sb, u_st, w, bias, (const __nv_bfloat16*)state, lines,
                                                            ctx_len, q_len, y, T, C, K, silu);
@@ -885,7 +885,7 @@ void ssd_scan_launch(const SsdScanParams& p, bool lp, cudaStream_t st) {
 
 void group_rmsnorm_launch(const float* y, const float* w, void* out, bool out_lp, int rows, int W, int groups, float eps, cudaStream_t st) {
   if (rows <= 0) return;
-  dim3 grid(groups, rows);
+  dim3 grid(rows, groups);
   if (out_lp)
     group_rmsnorm_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(y, w, (__nv_bfloat16*)out, W, W / groups, eps);
   else

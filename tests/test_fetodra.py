@@ -408,6 +408,13 @@ def test_gpu_kernels_match_definitions_on_ragged_rows():
         d = ops.ssd_scan(xBC.to(dev), pz.to(dev)[..., inner:inner + nh], pz.to(dev)[..., :inner], Al.to(dev), db.to(dev), Dk.to(dev), S2,
                          lines.to(dev), ctx.to(dev), ql.to(dev), nh, P, N, G)
         assert torch.allclose(c * live, d.cpu() * live, atol=1e-4, rtol=1e-4) and torch.allclose(S1, S2.cpu(), atol=1e-4, rtol=1e-4)
+    # more rows / tokens than one grid axis other than x can index
+    yv, wg = rn(70000, 16), rn(16)
+    assert torch.allclose(ref.group_rmsnorm(yv, wg, 2, 1e-5), ops.group_rmsnorm(yv.to(dev), wg.to(dev), 2, 1e-5).cpu(), atol=1e-5)
+    u, wt, st = rn(1, 70000, 8), rn(8, 2), rn(2, 1, 8)
+    one, zero = torch.tensor([70000]).int(), torch.tensor([0]).int()
+    assert torch.allclose(ref.short_conv(u, wt, None, st, zero, zero, one), ops.short_conv(u.to(dev), wt.to(dev), None, st.to(dev), zero.to(dev), zero.to(dev),
+                                                                                           one.to(dev)).cpu(), atol=1e-5)
 
 
 @pytest.mark.gpu
