@@ -1,0 +1,200 @@
+// Two-matrix experts y = W_down act(W_up x) for activations in bf16 or fp32 and for any sizes: the CUDA-core companion of the grouped
+// tcgen05 path (moe_grouped.cu), which needs bf16 and sizes in multiples of 64.  The permutation is the same one (moe_plan_kernel:
+// every expert's rows padded to whole 128-row tiles, static row bound, no host synchronisation):
+//
+//   gather    xp[row] = x[token(row)], zero rows for padding
+//   GEMM 1    h = act(xp W_up[e]^T)       64 x 64 output tiles, fp32 accumulation, the expert of a tile from the tile table
+//   GEMM 2    y = h W_down[e]^T
+//   combine   out[token] = sum_slot affinity * y[pos[token, slot]]     (fp32, fixed slot order)
+//
+// and for a handful of tokens (decode steps) two weight-streaming kernels without any permutation: one warp per (entry, hidden unit),
+// then one warp per (token, output channel) that walks the token's chosen experts.  Compiled WITHOUT fast-math: the fp32 instantiation
+// is the exact-arithmetic path.
+#include <cuda_bf16.h>
+
+#include <stdexcept>
+#include <type_traits>
+
+#include "common.cuh"
+#include "seqmix.h"
+
+namespace nxdi {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldx(const T* p);
+template <> __device__ __forceinline__ float ldx<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldx<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stx(T* p, float v);
+template <> __device__ __forceinline__ void stx<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stx<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float act_apply(int act, float v) {
+  switch (act) {
+    case 1: return fmaxf(v, 0.f);
+    case 2: { const float r = fmaxf(v, 0.f); return r * r; }
+    case 3: return v / (1.f + expf(-v));
+    case 4: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    default: return v;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) gather_kernel(const T* __restrict__ x, const int* __restrict__ row_entry,
+                                                     const int* __restrict__ tile_expert, T* __restrict__ xp, int H, int k) {
+  const int r = blockIdx.x;
+  if (tile_expert[r >> 7] < 0) return;
+  const int ent = row_entry[r];
+  T* dst = xp + (size_t)r * H;
+  if (ent < 0) {
+    for (int c = threadIdx.x; c < H; c += 128) stx(dst + c, 0.f);
+    return;
+  }
+  const T* src = x + (size_t)(ent / k) * H;
+  for (int c = threadIdx.x; c < H; c += 128) dst[c] = src[c];
+}
+
+// C[r, n] = act(sum_k A[r, k] * W[e, n, k]); block = 64 x 64 outputs, 256 threads x (4 x 4), k in slices of 16
+constexpr int PT = 64, PK = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) grouped_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, T* __restrict__ C, int N, int K,
+                                                           int act, const int* __restrict__ tile_expert) {
+  const int r0 = blockIdx.y * PT, n0 = blockIdx.x * PT;
+  const int e = tile_expert[r0 >> 7];
+  if (e < 0) return;
+  __shared__ float As[PK][PT + 1], Ws[PK][PT + 1];
+  const T* Wb = W + (size_t)e * N * K;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += PK) {
+    for (int i = threadIdx.x; i < PT * PK; i += 256) {
+      const int rr = i / PK, kk = i % PK;
+      const bool ink = k0 + kk < K;
+      As[kk][rr] = ink ? ldx(A + (size_t)(r0 + rr) * K + k0 + kk) : 0.f;
+      Ws[kk][rr] = (ink && n0 + rr < N) ? ldx(Wb + (size_t)(n0 + rr) * K + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < PK; ++kk) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; w[i] = Ws[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) stx(C + (size_t)(r0 + ty * 4 + i) * N + n, act_apply(act, acc[i][j]));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) combine_kernel(const T* __restrict__ y, const float* __restrict__ topk_w, const int* __restrict__ pos,
+                                                      T* __restrict__ out, int H, int k) {
+  const int tok = blockIdx.x;
+  __shared__ int s_pos[64];
+  __shared__ float s_w[64];
+  if ((int)threadIdx.x < k) {
+    s_pos[threadIdx.x] = pos[(size_t)tok * k + threadIdx.x];
+    s_w[threadIdx.x] = topk_w[(size_t)tok * k + threadIdx.x];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += 128) {
+    float f = 0.f;
+    for (int s = 0; s < k; ++s)
+      if (s_pos[s] >= 0) f += s_w[s] * ldx(y + (size_t)s_pos[s] * H + c);
+    stx(out + (size_t)tok * H + c, f);
+  }
+}
+
+// dot product of two dense rows by one warp (every lane gets the sum)
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* a, const T* b, int n, int lane) {
+  float s = 0.f;
+  for (int c = lane; c < n; c += 32) s = fmaf(ldx(a + c), ldx(b + c), s);
+  return warp_sum(s);
+}
+
+// h[entry, i] = act(x[token] . W_up[e, i, :]); one warp per (entry, i)
+template <typename T>
+__global__ void __launch_bounds__(256) decode_up_kernel(const T* __restrict__ x, const T* __restrict__ w_up, const int* __restrict__ topk_i,
+                                                        T* __restrict__ h, int entries, int k, int H, int I, int expert_offset, int e_local,
+                                                        int act) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (long long)entries * I) return;
+  const int ent = (int)(wid / I), i = (int)(wid % I);
+  const int e = topk_i[ent] - expert_offset;
+  if (e < 0 || e >= e_local) return;
+  const float v = warp_dot(x + (size_t)(ent / k) * H, w_up + ((size_t)e * I + i) * H, H, lane);
+  if (lane == 0) stx(h + (size_t)ent * I + i, act_apply(act, v));
+}
+
+// out[token, n] = sum_slot affinity * round(h[entry] . W_down[e, n, :]); one warp per (token, n)
+template <typename T>
+__global__ void __launch_bounds__(256) decode_down_kernel(const T* __restrict__ h, const T* __restrict__ w_down, const float* __restrict__ topk_w,
+                                                          const int* __restrict__ topk_i, T* __restrict__ out, int N, int k, int H, int I,
+                                                          int expert_offset, int e_local) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (long long)N * H) return;
+  const int tok = (int)(wid / H), n = (int)(wid % H);
+  float f = 0.f;
+  for (int s = 0; s < k; ++s) {
+    const int ent = tok * k + s, e = topk_i[ent] - expert_offset;
+    if (e < 0 || e >= e_local) continue;
+    float v = warp_dot(h + (size_t)ent * I, w_down + ((size_t)e * H + n) * I, I, lane);
+    if constexpr (!std::is_same<T, float>::value) v = __bfloat162float(__float2bfloat16_rn(v));     // the expert's output in the activation type
+    f += topk_w[ent] * v;
+  }
+  if (lane == 0) stx(out + (size_t)tok * H + n, f);
+}
+
+}  // namespace
+
+void moe_plain_gather_launch(const void* x, const int* row_entry, const int* tile_expert, void* xp, int R, int H, int k, bool lp, cudaStream_t st) {
+  if (R <= 0) return;
+  if (lp) gather_kernel<__nv_bfloat16><<<R, 128, 0, st>>>((const __nv_bfloat16*)x, row_entry, tile_expert, (__nv_bfloat16*)xp, H, k);
+  else gather_kernel<float><<<R, 128, 0, st>>>((const float*)x, row_entry, tile_expert, (float*)xp, H, k);
+}
+
+void moe_plain_gemm_launch(const void* a, const void* w, void* c, int R, int N, int K, int act, const int* tile_expert, bool lp, cudaStream_t st) {
+  if (R <= 0 || N <= 0) return;
+  if (R % 128 != 0) throw std::runtime_error("moe_plain_gemm: the row bound must be a multiple of 128");
+  if (R / PT > 65535) throw std::runtime_error("moe_plain_gemm: too many row tiles");
+  dim3 grid((N + PT - 1) / PT, R / PT);
+  if (lp) grouped_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)c, N, K, act, tile_expert);
+  else grouped_gemm_kernel<float><<<grid, 256, 0, st>>>((const float*)a, (const float*)w, (float*)c, N, K, act, tile_expert);
+}
+
+void moe_plain_combine_launch(const void* y, const float* topk_w, const int* pos, void* out, int N, int H, int k, bool lp, cudaStream_t st) {
+  if (N <= 0) return;
+  if (k > 64) throw std::runtime_error("moe_plain_combine: top-k > 64");
+  if (lp) combine_kernel<__nv_bfloat16><<<N, 128, 0, st>>>((const __nv_bfloat16*)y, topk_w, pos, (__nv_bfloat16*)out, H, k);
+  else combine_kernel<float><<<N, 128, 0, st>>>((const float*)y, topk_w, pos, (float*)out, H, k);
+}
+
+void moe_plain_decode_launch(const void* x, const void* w_up, const void* w_down, const float* topk_w, const int* topk_i, void* h, void* out,
+                             int N, int k, int H, int I, int expert_offset, int e_local, int act, bool lp, cudaStream_t st) {
+  if (N <= 0) return;
+  const long long w1 = (long long)N * k * I, w2 = (long long)N * H;
+  const unsigned g1 = (unsigned)((w1 + 7) / 8), g2 = (unsigned)((w2 + 7) / 8);
+  if (lp) {
+    decode_up_kernel<__nv_bfloat16><<<g1, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_up, topk_i, (__nv_bfloat16*)h, N * k, k, H, I,
+                                                        expert_offset, e_local, act);
+    decode_down_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)w_down, topk_w, topk_i, (__nv_bfloat16*)out, N, k,
+                                                          H, I, expert_offset, e_local);
+  } else {
+    decode_up_kernel<float><<<g1, 256, 0, st>>>((const float*)x, (const float*)w_up, topk_i, (float*)h, N * k, k, H, I, expert_offset, e_local, act);
+    decode_down_kernel<float><<<g2, 256, 0, st>>>((const float*)h, (const float*)w_down, topk_w, topk_i, (float*)out, N, k, H, I, expert_offset,
+                                                  e_local);
+  }
+}
+
+}  // namespace nxdi

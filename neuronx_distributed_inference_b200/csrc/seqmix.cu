@@ -385,16 +385,20 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
         if (dv < Dv) acc[i] += pw[dv] * f;
       }
     }
+    m = M;
   }
+  if (p.sinks) l += expf(p.sinks[h] - m);      // the sink: one more term of the denominator, no value (a live query sees itself: m is finite)
   const float inv = 1.f / l;
   T* orow = (T*)p.out + qi * Dv;
-  const T* grow = p.gate ? (const T*)p.gate + (long long)b * p.g_sb + (long long)t * p.g_st + (long long)h * Dv : nullptr;
+  const T* grow = p.gate ? (const T*)p.gate + (long long)b * p.g_sb + (long long)t * p.g_st + (p.gate_per_head ? (long long)h : (long long)h * Dv)
+                         : nullptr;
+  const float head_gate = (grow && p.gate_per_head) ? sigmoidf_acc(ldf(grow)) : 1.f;
 #pragma unroll
   for (int i = 0; i < ATT_VPL; ++i) {
     const int dv = lane + 32 * i;
     if (dv < Dv) {
-      float o = acc[i] * inv;
-      if (grow) o *= sigmoidf_acc(ldf(grow + dv));
+      float o = acc[i] * inv * head_gate;
+      if (grow && !p.gate_per_head) o *= sigmoidf_acc(ldf(grow + dv));
       stf(orow + dv, o);
     }
   }
@@ -563,9 +567,19 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float i0 = 1.f / l0, i1 = 1.f / l1;
+  if (p.sinks) {                             // rows past q_len have m = -inf and are never stored
+    const float sk = p.sinks[h];
+    l0 += __expf(sk - m0);
+    l1 += __expf(sk - m1);
+  }
+  float i0 = 1.f / l0, i1 = 1.f / l1;
   __nv_bfloat16* ob = (__nv_bfloat16*)p.out + ((long long)b * p.T * p.Hq + h) * DV;
-  const __nv_bfloat16* gb = p.gate ? (const __nv_bfloat16*)p.gate + (long long)b * p.g_sb + (long long)h * DV : nullptr;
+  const __nv_bfloat16* gb = (p.gate && !p.gate_per_head) ? (const __nv_bfloat16*)p.gate + (long long)b * p.g_sb + (long long)h * DV : nullptr;
+  if (p.gate && p.gate_per_head) {
+    const __nv_bfloat16* gh = (const __nv_bfloat16*)p.gate + (long long)b * p.g_sb + h;
+    if (r0 < qn) i0 *= sigmoidf_acc(__bfloat162float(gh[(long long)r0 * p.g_st]));
+    if (r1 < qn) i1 *= sigmoidf_acc(__bfloat162float(gh[(long long)r1 * p.g_st]));
+  }
 #pragma unroll
   for (int nv = 0; nv < DV / 8; ++nv) {
     const int col = nv * 8 + tig * 2;
@@ -777,6 +791,86 @@ __global__ void __launch_bounds__(256) clamped_glu_vec_kernel(const T* __restric
   *reinterpret_cast<uint4*>(out + r * F + c) = o;
 }
 
+// ---- fp32 residual stream: s = [x] + [y1] + [y2] + [rms_unit(yn) * wn] + [vec]; h = rms_unit(s) * w -------------------------------
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256) stream_add_rmsnorm_kernel(StreamAddParams p) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int W = p.W;
+  const float* xr = p.x ? p.x + row * W : nullptr;
+  const TY* y1 = p.y1 ? (const TY*)p.y1 + row * W : nullptr;
+  const TY* y2 = p.y2 ? (const TY*)p.y2 + row * W : nullptr;
+  const TY* yn = p.yn ? (const TY*)p.yn + row * W : nullptr;
+  float rn = 0.f;
+  if (yn) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float v = ldf(yn + c); ss += v * v; }
+    rn = 1.f / sqrtf(block_sum(ss, red) / (float)W + p.eps);
+  }
+  float* so = p.s + row * W;
+  __nv_bfloat16* slp = p.s_lp ? (__nv_bfloat16*)p.s_lp + row * W : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float s = xr ? xr[c] : 0.f;
+    if (y1) s += ldf(y1 + c);
+    if (y2) s += ldf(y2 + c);
+    if (yn) s += ldf(yn + c) * rn * (p.wn ? p.wn[c] : 1.f);
+    if (p.vec) s += p.vec[c];
+    so[c] = s;
+    if (slp) slp[c] = __float2bfloat16_rn(s);
+    ss += s * s;
+  }
+  if (!p.h) return;
+  const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + p.eps);
+  TH* ho = (TH*)p.h + row * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) stf(ho + c, so[c] * r * p.w[c]);      // a thread re-reads only what it wrote itself
+}
+
+// ---- latent row: RMS norm of a slice of the projection + paged cache write ----------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) latent_norm_append_kernel(const T* __restrict__ p, long long p_sb, long long p_st, const float* __restrict__ w,
+                                                                 T* __restrict__ cache, const int* __restrict__ block_table,
+                                                                 const int* __restrict__ ctx_len, const int* __restrict__ q_len, int R, int page,
+                                                                 int max_blocks, float eps) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, b = blockIdx.y;
+  if (t >= q_len[b]) return;
+  const T* row = p + (long long)b * p_sb + (long long)t * p_st;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) { const float v = ldf(row + c); ss += v * v; }
+  const float r = 1.f / sqrtf(block_sum(ss, red) / (float)R + eps);
+  const int pos = ctx_len[b] + t;
+  T* dst = cache + ((long long)block_table[(long long)b * max_blocks + pos / page] * page + pos % page) * R;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) stf(dst + c, ldf(row + c) * r * w[c]);
+}
+
+// ---- elementwise activations -------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float unary_apply(int act, float v) {
+  switch (act) {
+    case 1: return fmaxf(v, 0.f);
+    case 2: { const float r = fmaxf(v, 0.f); return r * r; }
+    case 3: return v / (1.f + expf(-v));
+    case 4: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    default: return v;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gated_act_mul_kernel(const T* __restrict__ gate, const T* __restrict__ other, long long o_stride,
+                                                            T* __restrict__ out, long long rows, int C, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * C) return;
+  const long long r = i / C;
+  const int c = (int)(i % C);
+  stf(out + i, unary_apply(act, ldf(gate + i)) * ldf(other + r * o_stride + c));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) stf(out + i, unary_apply(act, ldf(x + i)));
+}
+
 template <typename K>
 void opt_in_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -791,6 +885,50 @@ void scaled_add_rmsnorm_launch(const float* x, const void* y, bool y_lp, const f
     scaled_add_rmsnorm_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(x, (const __nv_bfloat16*)y, w, out, (__nv_bfloat16*)out_lp, W, alpha, eps, offset);
   else
     scaled_add_rmsnorm_kernel<float><<<rows, 256, 0, st>>>(x, (const float*)y, w, out, (__nv_bfloat16*)out_lp, W, alpha, eps, offset);
+}
+
+void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, cudaStream_t st) {
+  if (p.rows <= 0) return;
+  const int threads = p.W >= 1024 ? 256 : 128;
+  if (y_lp) {
+    if (h_lp) stream_add_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16><<<p.rows, threads, 0, st>>>(p);
+    else stream_add_rmsnorm_kernel<__nv_bfloat16, float><<<p.rows, threads, 0, st>>>(p);
+  } else {
+    if (h_lp) stream_add_rmsnorm_kernel<float, __nv_bfloat16><<<p.rows, threads, 0, st>>>(p);
+    else stream_add_rmsnorm_kernel<float, float><<<p.rows, threads, 0, st>>>(p);
+  }
+}
+
+void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, const float* w, void* cache, const int* block_table,
+                               const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
+                               cudaStream_t st) {
+  if (B <= 0 || T <= 0) return;
+  dim3 grid(T, B);
+  if (lp)
+    latent_norm_append_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)p, p_sb, p_st, w, (__nv_bfloat16*)cache, block_table, ctx_len,
+                                                                   q_len, R, page, max_blocks, eps);
+  else
+    latent_norm_append_kernel<float><<<grid, 128, 0, st>>>((const float*)p, p_sb, p_st, w, (float*)cache, block_table, ctx_len, q_len, R, page,
+                                                           max_blocks, eps);
+}
+
+void gated_act_mul_launch(const void* gate, const void* other, long long o_stride, void* out, long long rows, int C, int act, bool lp,
+                          cudaStream_t st) {
+  const long long n = rows * C;
+  if (n <= 0) return;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (lp)
+    gated_act_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)other, o_stride, (__nv_bfloat16*)out,
+                                                              rows, C, act);
+  else
+    gated_act_mul_kernel<float><<<grid, 256, 0, st>>>((const float*)gate, (const float*)other, o_stride, (float*)out, rows, C, act);
+}
+
+void unary_act_launch(const void* x, void* out, long long n, int act, bool lp, cudaStream_t st) {
+  if (n <= 0) return;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (lp) unary_act_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, act);
+  else unary_act_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (float*)out, n, act);
 }
 
 void short_conv_launch(const void* u, long long u_sb, long long u_st, const float* w, const float* bias, const void* state,

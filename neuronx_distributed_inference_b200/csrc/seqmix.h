@@ -14,6 +14,36 @@ constexpr int SEQMIX_MAX_STATE = 256;    // scan: state size per head
 void scaled_add_rmsnorm_launch(const float* x, const void* y, bool y_lp, const float* w, float* out, void* out_lp, int rows, int W,
                                float alpha, float eps, float offset, cudaStream_t st);
 
+// fp32 residual stream update and the norm that reads it: s = [x] + [y1] + [y2] + [rms_unit(yn) * wn] + [vec], h = rms_unit(s) * w.
+// y1 / y2 / yn share one activation type; every input is optional except that at least one row source is present.
+struct StreamAddParams {
+  const float* x;                  // [rows, W] or null
+  const void *y1, *y2, *yn;        // [rows, W] or null
+  const float *wn, *vec, *w;       // [W] or null (w is required when h is wanted)
+  float* s;                        // [rows, W]
+  void* s_lp;                      // bf16 copy of s, or null
+  void* h;                         // normalised rows (bf16 or fp32), or null
+  int rows, W;
+  float eps;
+};
+void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, cudaStream_t st);
+
+void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, const float* w, void* cache, const int* block_table,
+                               const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
+                               cudaStream_t st);
+
+// act codes: 1 relu, 2 relu^2, 3 silu, 4 tanh-gelu
+void gated_act_mul_launch(const void* gate, const void* other, long long o_stride, void* out, long long rows, int C, int act, bool lp,
+                          cudaStream_t st);
+void unary_act_launch(const void* x, void* out, long long n, int act, bool lp, cudaStream_t st);
+
+// Two-matrix experts y = W_down act(W_up x) on a device-side permutation (moe_plain.cu); T = bf16 or fp32, any sizes.
+void moe_plain_gather_launch(const void* x, const int* row_entry, const int* tile_expert, void* xp, int R, int H, int k, bool lp, cudaStream_t st);
+void moe_plain_gemm_launch(const void* a, const void* w, void* c, int R, int N, int K, int act, const int* tile_expert, bool lp, cudaStream_t st);
+void moe_plain_combine_launch(const void* y, const float* topk_w, const int* pos, void* out, int N, int H, int k, bool lp, cudaStream_t st);
+void moe_plain_decode_launch(const void* x, const void* w_up, const void* w_down, const float* topk_w, const int* topk_i, void* h, void* out,
+                             int N, int k, int H, int I, int expert_offset, int e_local, int act, bool lp, cudaStream_t st);
+
 void short_conv_launch(const void* u, long long u_sb, long long u_st, const float* w, const float* bias, const void* state,
                        const int* lines, const int* ctx_len, const int* q_len, float* y, int B, int T, int C, int K, bool silu, bool lp,
                        cudaStream_t st);
@@ -46,6 +76,8 @@ struct WindowAttnParams {
   void* out;                // [B, T, Hq * Dv]
   int B, T, Hq, G, D, Dv, page, max_blocks, window, keep_first;
   float scale, softcap;
+  const float* sinks;       // [Hq] or null: exp(sinks[h]) joins the softmax denominator of head h (no key, no value)
+  int gate_per_head;        // 1: gate is [B, T, Hq], one sigmoid factor per head instead of one per output channel
 };
 void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStream_t st);
 

@@ -3,6 +3,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include "api.h"
 #include "seqmix.h"
 
 namespace nxdi {
@@ -143,7 +144,7 @@ at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w
 
 at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table,
                                   const at::Tensor& ctx, const at::Tensor& qlen, double scale, double softcap, int64_t window,
-                                  int64_t keep_first, const OptT& gate) {
+                                  int64_t keep_first, const OptT& gate, const OptT& sinks, bool gate_per_head) {
   check_act(q, "paged_window_attention q");
   TORCH_CHECK(q.dim() == 4 && q.is_contiguous());
   const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), D = q.size(3);
@@ -159,8 +160,15 @@ at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache
   WindowAttnParams a{};
   if (gate.has_value()) {
     check_rows(*gate, "gate");
-    TORCH_CHECK(gate->is_cuda() && gate->scalar_type() == q.scalar_type() && gate->size(0) == B && gate->size(1) == T && gate->size(2) == Hq * Dv);
+    TORCH_CHECK(gate->is_cuda() && gate->scalar_type() == q.scalar_type() && gate->size(0) == B && gate->size(1) == T &&
+                gate->size(2) == (gate_per_head ? Hq : Hq * Dv), "gate: [B, T, heads * value size], or [B, T, heads] with gate_per_head");
     a.gate = gate->data_ptr(); a.g_sb = gate->stride(0); a.g_st = gate->stride(1);
+    a.gate_per_head = gate_per_head ? 1 : 0;
+  }
+  if (sinks.has_value()) {
+    check_f32(*sinks, "sinks");
+    TORCH_CHECK(sinks->numel() == Hq, "sinks: one per query head");
+    a.sinks = sinks->data_ptr<float>();
   }
   c10::cuda::CUDAGuard guard(q.device());
   auto out = at::zeros({B, T, Hq * Dv}, q.options());
@@ -224,9 +232,147 @@ at::Tensor clamped_glu(const at::Tensor& gu, double limit, double alpha) {
   return out;
 }
 
+std::tuple<at::Tensor, OptT, OptT> stream_add_rmsnorm(const OptT& x, const OptT& y1, const OptT& y2, const OptT& yn, const OptT& wn,
+                                                      const OptT& vec, const OptT& w, double eps, bool h_lp, bool want_s_lp) {
+  const at::Tensor* first = x.has_value() ? &*x : (y1.has_value() ? &*y1 : (yn.has_value() ? &*yn : nullptr));
+  TORCH_CHECK(first != nullptr && first->dim() == 2, "stream_add_rmsnorm: at least one [rows, W] input");
+  const int64_t rows = first->size(0), W = first->size(1);
+  if (x.has_value()) {
+    check_f32(*x, "stream_add_rmsnorm x");
+    TORCH_CHECK(x->sizes() == first->sizes());
+  }
+  bool y_lp = false, seen = false;
+  for (const OptT* y : {&y1, &y2, &yn}) {
+    if (!y->has_value()) continue;
+    check_act(**y, "stream_add_rmsnorm addend");
+    TORCH_CHECK((*y)->is_contiguous() && (*y)->sizes() == first->sizes());
+    TORCH_CHECK(!seen || y_lp == is_lp(**y), "stream_add_rmsnorm: addends of one type");
+    y_lp = is_lp(**y);
+    seen = true;
+  }
+  for (const OptT* v : {&wn, &vec, &w}) {
+    if (!v->has_value()) continue;
+    check_f32(**v, "stream_add_rmsnorm vector");
+    TORCH_CHECK((*v)->numel() == W);
+  }
+  c10::cuda::CUDAGuard guard(first->device());
+  auto f32 = first->options().dtype(at::kFloat);
+  auto s = at::empty({rows, W}, f32);
+  OptT s_lp, h;
+  if (want_s_lp) s_lp = at::empty({rows, W}, f32.dtype(at::kBFloat16));
+  if (w.has_value()) h = at::empty({rows, W}, f32.dtype(h_lp ? at::kBFloat16 : at::kFloat));
+  StreamAddParams a{};
+  a.x = x.has_value() ? x->data_ptr<float>() : nullptr;
+  a.y1 = y1.has_value() ? y1->data_ptr() : nullptr;
+  a.y2 = y2.has_value() ? y2->data_ptr() : nullptr;
+  a.yn = yn.has_value() ? yn->data_ptr() : nullptr;
+  a.wn = wn.has_value() ? wn->data_ptr<float>() : nullptr;
+  a.vec = vec.has_value() ? vec->data_ptr<float>() : nullptr;
+  a.w = w.has_value() ? w->data_ptr<float>() : nullptr;
+  a.s = s.data_ptr<float>();
+  a.s_lp = s_lp.has_value() ? s_lp->data_ptr() : nullptr;
+  a.h = h.has_value() ? h->data_ptr() : nullptr;
+  a.rows = (int)rows; a.W = (int)W; a.eps = (float)eps;
+  stream_add_rmsnorm_launch(a, y_lp, h_lp, stream());
+  return {s, s_lp, h};
+}
+
+void latent_norm_append(const at::Tensor& p, int64_t offset, int64_t rank, const at::Tensor& w, double eps, at::Tensor cache,
+                        const at::Tensor& block_table, const at::Tensor& ctx, const at::Tensor& qlen) {
+  check_act(p, "latent_norm_append input");
+  check_rows(p, "latent_norm_append input");
+  const int64_t B = p.size(0), T = p.size(1);
+  TORCH_CHECK(offset >= 0 && rank >= 1 && offset + rank <= p.size(2), "latent_norm_append: slice outside the row");
+  check_f32(w, "latent norm weight");
+  TORCH_CHECK(w.numel() == rank);
+  TORCH_CHECK(cache.is_cuda() && cache.scalar_type() == p.scalar_type() && cache.is_contiguous() && cache.dim() == 4 && cache.size(2) == 1 &&
+              cache.size(3) == rank, "latent cache [blocks, page, 1, rank] of the activation type");
+  TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == at::kInt && block_table.is_contiguous() && block_table.dim() == 2 &&
+              block_table.size(0) == B);
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+  c10::cuda::CUDAGuard guard(p.device());
+  const char* base = (const char*)p.data_ptr() + offset * p.element_size();
+  latent_norm_append_launch(base, p.stride(0), p.stride(1), w.data_ptr<float>(), cache.data_ptr(), block_table.data_ptr<int>(), ctx.data_ptr<int>(),
+                            qlen.data_ptr<int>(), (int)B, (int)T, (int)rank, (int)cache.size(1), (int)block_table.size(1), (float)eps, is_lp(p),
+                            stream());
+}
+
+at::Tensor gated_act_mul(const at::Tensor& gate, const at::Tensor& other, int64_t act) {
+  check_act(gate, "gated_act_mul gate");
+  TORCH_CHECK(gate.dim() == 2 && gate.is_contiguous() && other.is_cuda() && other.scalar_type() == gate.scalar_type() && other.dim() == 2 &&
+              other.sizes() == gate.sizes() && other.stride(1) == 1, "gated_act_mul: [rows, C] inputs of one type, the second with a row stride");
+  c10::cuda::CUDAGuard guard(gate.device());
+  auto out = at::empty_like(gate);
+  gated_act_mul_launch(gate.data_ptr(), other.data_ptr(), other.stride(0), out.data_ptr(), gate.size(0), (int)gate.size(1), (int)act, is_lp(gate),
+                       stream());
+  return out;
+}
+
+at::Tensor unary_act(const at::Tensor& x, int64_t act) {
+  check_act(x, "unary_act input");
+  TORCH_CHECK(x.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = at::empty_like(x);
+  unary_act_launch(x.data_ptr(), out.data_ptr(), x.numel(), (int)act, is_lp(x), stream());
+  return out;
+}
+
+// Routed two-matrix experts: x [N, H], w_up [E, I, H], w_down [E, H, I] (activation type), topk_w fp32 / topk_i int32 [N, k].
+// `tc`: bf16 with H and I in multiples of 64 -> grouped tcgen05 GEMMs, the activation as an elementwise pass between them.
+at::Tensor moe_plain(const at::Tensor& x, const at::Tensor& w_up, const at::Tensor& w_down, const at::Tensor& topk_w, const at::Tensor& topk_i,
+                     int64_t expert_offset, int64_t act, bool tc) {
+  check_act(x, "moe_plain x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && w_up.dim() == 3 && w_down.dim() == 3 && w_up.is_contiguous() && w_down.is_contiguous() &&
+              w_up.scalar_type() == x.scalar_type() && w_down.scalar_type() == x.scalar_type() && w_up.is_cuda() && w_down.is_cuda());
+  const int N = (int)x.size(0), H = (int)x.size(1), E = (int)w_up.size(0), I = (int)w_up.size(1), k = (int)topk_i.size(1);
+  TORCH_CHECK(w_up.size(2) == H && w_down.size(0) == E && w_down.size(1) == H && w_down.size(2) == I, "moe_plain: w_up [E, I, H], w_down [E, H, I]");
+  TORCH_CHECK(topk_w.is_cuda() && topk_w.scalar_type() == at::kFloat && topk_i.is_cuda() && topk_i.scalar_type() == at::kInt && topk_w.is_contiguous() &&
+              topk_i.is_contiguous() && topk_w.numel() == (int64_t)N * k && topk_i.size(0) == N && k <= 64 && E <= 512);
+  const bool lp = is_lp(x);
+  TORCH_CHECK(!tc || (lp && H % 64 == 0 && I % 64 == 0), "moe_plain: the tensor-core path needs bf16 and sizes in multiples of 64");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto st = stream();
+  auto out = at::empty({N, H}, x.options());
+  if (N * k <= 32) {        // decode steps: weight-streaming kernels, no permutation
+    auto h = at::empty({(int64_t)N * k, I}, x.options());
+    moe_plain_decode_launch(x.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), topk_w.data_ptr<float>(), topk_i.data_ptr<int>(), h.data_ptr(),
+                            out.data_ptr(), N, k, H, I, (int)expert_offset, E, (int)act, lp, st);
+    return out;
+  }
+  const int64_t R = (((int64_t)N * k + (int64_t)E * 127) + 127) / 128 * 128;   // static bound: graph-stable shapes
+  auto iopt = x.options().dtype(at::kInt);
+  auto pos = at::empty({(int64_t)N * k}, iopt);
+  auto row_entry = at::empty({R}, iopt);
+  auto tile_expert = at::empty({R / 128}, iopt);
+  auto xp = at::empty({R, H}, x.options());
+  auto h = at::empty({R, I}, x.options());
+  auto y = at::empty({R, H}, x.options());
+  moe_plan_launch(topk_i.data_ptr<int>(), N * k, (int)expert_offset, E, (int)R, pos.data_ptr<int>(), row_entry.data_ptr<int>(),
+                  tile_expert.data_ptr<int>(), st);
+  if (tc) {
+    moe_gather_launch(x.data_ptr(), topk_w.data_ptr<float>(), row_entry.data_ptr<int>(), tile_expert.data_ptr<int>(), xp.data_ptr(), (int)R, H, k, 0, st);
+    gemm_grouped_launch(xp.data_ptr(), w_up.data_ptr(), nullptr, h.data_ptr(), (int)R, I, H, E, 0, tile_expert.data_ptr<int>(), nullptr, nullptr, st);
+    unary_act_launch(h.data_ptr(), h.data_ptr(), (long long)R * I, (int)act, true, st);      // rows of unused tiles hold junk; nothing reads them
+    gemm_grouped_launch(h.data_ptr(), w_down.data_ptr(), nullptr, y.data_ptr(), (int)R, H, I, E, 0, tile_expert.data_ptr<int>(), nullptr, nullptr, st);
+    moe_combine_launch(y.data_ptr(), topk_w.data_ptr<float>(), pos.data_ptr<int>(), out.data_ptr(), N, H, k, 0, st);
+    return out;
+  }
+  moe_plain_gather_launch(x.data_ptr(), row_entry.data_ptr<int>(), tile_expert.data_ptr<int>(), xp.data_ptr(), (int)R, H, k, lp, st);
+  moe_plain_gemm_launch(xp.data_ptr(), w_up.data_ptr(), h.data_ptr(), (int)R, I, H, (int)act, tile_expert.data_ptr<int>(), lp, st);
+  moe_plain_gemm_launch(h.data_ptr(), w_down.data_ptr(), y.data_ptr(), (int)R, H, I, 0, tile_expert.data_ptr<int>(), lp, st);
+  moe_plain_combine_launch(y.data_ptr(), topk_w.data_ptr<float>(), pos.data_ptr<int>(), out.data_ptr(), N, H, k, lp, st);
+  return out;
+}
+
 }  // namespace
 
 void register_seqmix(pybind11::module_& m) {
+  m.def("stream_add_rmsnorm", &stream_add_rmsnorm);
+  m.def("latent_norm_append", &latent_norm_append);
+  m.def("gated_act_mul", &gated_act_mul);
+  m.def("unary_act", &unary_act);
+  m.def("moe_plain", &moe_plain);
   m.def("scaled_add_rmsnorm", &scaled_add_rmsnorm);
   m.def("short_conv", &short_conv);
   m.def("short_conv_update", &short_conv_update);

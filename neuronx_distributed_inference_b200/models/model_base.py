@@ -104,6 +104,33 @@ class PostNormDecoderLayer(nn.Module):
         return h
 
 
+class ParallelDecoderLayer(nn.Module):
+    """Pre-norm block whose sublayers sit side by side: ``h = norm1(x)``, ``x <- x + mixer(h) + mlp(h)`` (one norm, both read it),
+    optionally followed by a per-layer token input ``x <- x + rms_unit(side(x)) * w`` (:class:`TokenSideInput`).  The residual stream
+    is fp32; every sum is one ``ops.stream_add_rmsnorm`` launch, and the last one of a block also applies what comes BEFORE the next
+    block's sublayers — an optional vector added to the stream and that block's ``norm1`` — so a block receives ``(x, h)`` and returns
+    the pair for its successor.  ``cache_index`` names the cache the mixer uses in this run (a block may run several times per
+    forward, each run with a cache of its own)."""
+    mlp_is_moe = False
+
+    def __init__(self, mixer: nn.Module, mlp: Optional[nn.Module], norm1: nn.Module, side: Optional[nn.Module] = None, layer_idx: int = 0):
+        super().__init__()
+        self.mixer, self.mlp, self.norm1, self.side, self.layer_idx = mixer, mlp, norm1, side, layer_idx
+
+    def forward(self, x, h, meta, kv_mgr, cache_index=None, next_weight=None, next_vec=None):
+        dtype, eps = meta.extras["act_dtype"], self.norm1.variance_epsilon
+        a = self.mixer(h, meta, kv_mgr, cache_index=cache_index)
+        f = self.mlp(h) if self.mlp is not None else None
+        if self.side is None:
+            x, _, hn = ops.stream_add_rmsnorm(x, (a, f), vec=next_vec, weight=next_weight, eps=eps, lp_dtype=dtype)
+            return x, hn
+        x, x_lp, _ = ops.stream_add_rmsnorm(x, (a, f), eps=eps, lp_dtype=dtype, emit_stream_lp=True)
+        y = self.side(x if x_lp is None else x_lp, meta)
+        x, _, hn = ops.stream_add_rmsnorm(x, normed=y, normed_weight=self.side.norm_weight, vec=next_vec, weight=next_weight, eps=eps,
+                                          lp_dtype=dtype)
+        return x, hn
+
+
 class NeuronBaseModel(nn.Module):
     """Generic causal decoder.  Subclass hooks: ``setup_attr_for_model(config)`` (set
     ``tp_degree, hidden_size, num_attention_heads, num_key_value_heads, max_batch_size,
@@ -338,6 +365,10 @@ class NeuronBaseModel(nn.Module):
                 # every layer of the decode step in ONE persistent kernel (csrc/decode_step.cu)
                 h = decode_step.run_layers(self, h, meta)
                 mega = True
+        if not mega and hasattr(self, "run_layers"):
+            # stacks that do not visit ``self.layers`` once each in order (repeated spans, paired streams) walk them themselves
+            h = self.run_layers(h, meta)
+            mega = True
         for i, layer in enumerate(() if mega else self.layers):
             h = layer(h, meta, self.kv_mgr, lora=lora.for_layer(i)) if lora is not None else layer(h, meta, self.kv_mgr)
             if aux_layers is not None and i in aux_layers:

@@ -66,8 +66,9 @@ class PlainMLP(nn.Module):
         self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias, dtype=dtype, device=device,
                                      tensor_model_parallel_group=tp_group)
 
-    def forward(self, x, residual=None):
-        return self.fc2(ops.activation(self.fc1(x), self.act), residual)
+    def forward(self, x, residual=None, reduce: bool = True):
+        """``reduce`` is accepted for the shared-expert calling convention of :class:`MoE` (the row-parallel output is reduced either way)."""
+        return self.fc2(ops.unary_act(self.fc1(x), self.act), residual)
 
 
 class ClampedGLUMLP(nn.Module):

@@ -32,8 +32,11 @@ class RouterTopK(nn.Module):
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, dtype=torch.float32, act_fn: str = "softmax",
                  bias: bool = False, normalize_top_k_affinities: bool = True, apply_act_fn_over_topk: bool = False,
-                 device=None):
+                 device=None, renorm_eps: Optional[float] = None):
+        """``renorm_eps``: the chosen scores are divided by ``their sum + renorm_eps`` whatever ``act_fn`` is (sigmoid scores that are
+        renormalised over the chosen experts); ``None`` keeps the softmax-only ``normalize_top_k_affinities`` rule."""
         super().__init__()
+        self.renorm_eps = renorm_eps
         self.num_experts, self.top_k, self.act_fn = num_experts, top_k, act_fn
         self.normalize = normalize_top_k_affinities
         self.act_over_topk = apply_act_fn_over_topk
@@ -47,10 +50,10 @@ class RouterTopK(nn.Module):
             cd = self.compute_dtype
             logits = nn.functional.linear(x.to(cd), self.linear_router.weight.to(cd),
                                           None if self.linear_router.bias is None else self.linear_router.bias.to(cd)).float()
-            w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk)
+            w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
             return logits, w, idx
         logits = nn.functional.linear(x.float(), self.linear_router.weight, self.linear_router.bias)
-        w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk)
+        w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
         return logits, w, idx
 
 

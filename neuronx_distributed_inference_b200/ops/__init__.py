@@ -345,13 +345,22 @@ def sample(logits, top_k, top_p, temperature, rand=None, global_topk: int = 256)
     return ref.sample(logits, top_k, top_p, temperature, rand, global_topk)
 
 
-def moe_route(router_logits, top_k, act="softmax", normalize=True, act_over_topk=False):
-    return ref.moe_route(router_logits, top_k, act, normalize, act_over_topk)
+def moe_route(router_logits, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None):
+    return ref.moe_route(router_logits, top_k, act, normalize, act_over_topk, renorm_eps)
 
 
 def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_offset=0,
                 gate_up_bias=None, down_bias=None, act_fn=None, scale_input=False, gate_up_scale=None, down_scale=None):
     N = x.shape[0]
+    if (act in _MOE_PLAIN_ACTS and _mix_cuda(x) and act_fn is None and gate_up_scale is None and down_scale is None and gate_up_bias is None
+            and down_bias is None and not scale_input and w_gate_up.dtype == x.dtype and w_down.dtype == x.dtype and topk_i.dim() == 2
+            and topk_i.shape[1] <= 64 and w_gate_up.shape[0] <= 512 and w_gate_up.is_contiguous() and w_down.is_contiguous()):
+        # two-matrix experts ``down(act(up x))``: device-side permutation, grouped GEMMs with the activation in the first epilogue
+        # (tcgen05 for bf16 shapes in multiples of 64, a tiled CUDA-core kernel for fp32 and every other shape), weighted combine
+        stats["moe_plain"] += 1
+        tc = _MOE_GROUPED and x.dtype == torch.bfloat16 and x.shape[1] % 64 == 0 and w_down.shape[2] % 64 == 0 and N > GEMV_MAX_TOKENS
+        return _C().moe_plain(x.contiguous(), w_gate_up, w_down, topk_w.float().contiguous(), topk_i.to(torch.int32).contiguous(),
+                              int(expert_offset), _MOE_PLAIN_ACTS[act], bool(tc))
     if gate_up_scale is not None or down_scale is not None:
         # fp8 experts with dynamic activation quantisation asked for: W8A8 grouped GEMMs on the kind::f8f6f4 tensor-core path
         if (_use_cuda(x) and _MOE_GROUPED and _ACT_QUANT and N > GEMV_MAX_TOKENS and x.dtype == torch.bfloat16 and act in _MOE_ACTS
@@ -395,6 +404,8 @@ def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_off
 
 _MOE_GROUPED = os.environ.get("NXDI_B200_MOE_GROUPED", "1") == "1"
 _MOE_ACTS = {"silu_mul": 1, "gelu_tanh_mul": 2, "gelu_mul": 3, "gpt_oss_glu": 4}
+_UNARY_ACTS = {"relu": 1, "relu2": 2, "silu": 3, "gelu_tanh": 4}         # codes of csrc/seqmix.cu (unary_act, moe_plain, gated_act_mul)
+_MOE_PLAIN_ACTS = _UNARY_ACTS
 
 
 def rmsnorm_quant(x, weight, eps, clamp=float("inf"), offset: float = 0.0):
@@ -475,12 +486,15 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
                                        k_cache, v_cache, block_table, out_dtype)
 
 
-def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate=None):
+def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate=None, sinks=None,
+                           gate_per_head: bool = False):
     if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1) and v_cache.shape[-1] <= _MIX_MAX_VDIM:
         stats["paged_window_attention"] += 1
         return _C().paged_window_attention(q.contiguous(), k_cache, v_cache, _i32(block_table), _i32(ctx_len), _i32(q_len), float(scale),
-                                           float(softcap or 0.0), int(window or 0), int(keep_first or 0), gate)
-    return ref.paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate)
+                                           float(softcap or 0.0), int(window or 0), int(keep_first or 0), gate,
+                                           None if sinks is None else sinks.float().contiguous(), bool(gate_per_head))
+    return ref.paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate, sinks,
+                                      gate_per_head)
 
 
 def ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads, head_dim, n_state, n_groups):
@@ -507,3 +521,56 @@ def clamped_glu(gu, limit: float, alpha: float = 1.702):
         W = gu.shape[-1]
         return _C().clamped_glu(gu.reshape(-1, W).contiguous(), float(limit), float(alpha)).view(*gu.shape[:-1], W // 2)
     return ref.clamped_glu(gu, limit, alpha)
+
+
+def stream_add_rmsnorm(x, adds=(), normed=None, normed_weight=None, vec=None, weight=None, eps: float = 1e-6, lp_dtype=None,
+                       emit_stream_lp: bool = False):
+    """fp32 residual stream update + the norm that reads it, ONE kernel (definition: ops/reference.py)."""
+    adds = tuple(a for a in adds if a is not None)
+    first = x if x is not None else (adds[0] if adds else normed)
+    if (_use_cuda(first) and (x is None or x.dtype == torch.float32) and len(adds) <= 2 and all(a.dtype in _MIX_DTYPES for a in adds)
+            and (normed is None or normed.dtype in _MIX_DTYPES) and len({a.dtype for a in adds + ((normed,) if normed is not None else ())}) <= 1):
+        stats["stream_add_rmsnorm"] += 1
+        W = first.shape[-1]
+        lp = lp_dtype if lp_dtype not in (None, torch.float32) else None
+        flat = lambda t: None if t is None else t.reshape(-1, W).contiguous()          # noqa: E731
+        f32 = lambda t: None if t is None else t.float().contiguous()                  # noqa: E731
+        s, s_lp, h = _C().stream_add_rmsnorm(flat(x), flat(adds[0]) if adds else None, flat(adds[1]) if len(adds) > 1 else None, flat(normed),
+                                             f32(normed_weight), f32(vec), f32(weight), float(eps), lp == torch.bfloat16,
+                                             bool(emit_stream_lp and lp is not None))
+        shape = first.shape
+        return s.view(shape), (None if s_lp is None else s_lp.view(shape)), (None if h is None else h.view(shape))
+    return ref.stream_add_rmsnorm(x, adds, normed, normed_weight, vec, weight, eps, lp_dtype, emit_stream_lp)
+
+
+def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len):
+    if _mix_cuda(p) and p.stride(-1) == 1 and cache.dtype == p.dtype and cache.is_contiguous():
+        stats["latent_norm_append"] += 1
+        return _C().latent_norm_append(p, int(offset), int(rank), weight.float().contiguous(), float(eps), cache, _i32(block_table),
+                                       _i32(ctx_len), _i32(q_len))
+    return ref.latent_norm_append(p, offset, rank, weight, eps, cache, block_table, ctx_len, q_len)
+
+
+def gated_act_mul(gate, other, act: str = "gelu_tanh"):
+    if _mix_cuda(gate) and other.dtype == gate.dtype and other.stride(-1) == 1 and gate.is_contiguous() and act in _UNARY_ACTS \
+            and other.dim() == gate.dim() and other.shape == gate.shape:
+        stats["gated_act_mul"] += 1
+        C = gate.shape[-1]
+        o2 = other if other.dim() == 2 else other.reshape(-1, C) if other.is_contiguous() else _rows_view(other)
+        return _C().gated_act_mul(gate.reshape(-1, C), o2, _UNARY_ACTS[act]).view(gate.shape)
+    return ref.gated_act_mul(gate, other, act)
+
+
+def _rows_view(t):
+    """[B, T, C] slice of a wider contiguous row -> [B * T, C] with the wide row stride (no copy)."""
+    B, T, C = t.shape
+    if t.stride(0) == T * t.stride(1):
+        return t.as_strided((B * T, C), (t.stride(1), 1), t.storage_offset())
+    return t.reshape(-1, C)
+
+
+def unary_act(x, act: str):
+    if _mix_cuda(x) and act in _UNARY_ACTS and x.is_contiguous():
+        stats["unary_act"] += 1
+        return _C().unary_act(x.reshape(-1, x.shape[-1]), _UNARY_ACTS[act]).view(x.shape)
+    return ref.unary_act(x, act)

@@ -25,7 +25,7 @@ _tried = False
 
 GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # translation units whose results must match fp32 definitions closely: accurate tanh / exp / division instead of --use_fast_math
-PRECISE = {"seqmix.cu"}
+PRECISE = {"seqmix.cu", "moe_plain.cu"}
 
 
 def sources():

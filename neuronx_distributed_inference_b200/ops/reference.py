@@ -266,7 +266,7 @@ def argmax(logits):
 
 
 def moe_route(router_logits, top_k: int, act: str = "softmax", normalize: bool = True,
-              act_over_topk: bool = False):
+              act_over_topk: bool = False, renorm_eps=None):
     """-> (weights [N,top_k] fp32, expert ids [N,top_k]).  softmax-then-topk (Mixtral/DBRX/Qwen3),
     sigmoid (Llama-4) or topk-then-softmax (GPT-OSS ``apply_act_fn_over_topk``)."""
     x = router_logits.float()
@@ -276,7 +276,9 @@ def moe_route(router_logits, top_k: int, act: str = "softmax", normalize: bool =
         return w, i
     p = torch.softmax(x, -1) if act == "softmax" else torch.sigmoid(x)
     w, i = torch.topk(p, top_k, -1)
-    if normalize and act == "softmax":
+    if renorm_eps is not None:          # chosen scores divided by their sum (+ eps), whatever the activation
+        w = w / (w.sum(-1, keepdim=True) + renorm_eps)
+    elif normalize and act == "softmax":
         w = w / w.sum(-1, keepdim=True)
     return w, i
 
@@ -449,11 +451,12 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
 
 
 def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale: float, softcap: float, window: int,
-                           keep_first: int, gate=None):
+                           keep_first: int, gate=None, sinks=None, gate_per_head: bool = False):
     """Soft-capped attention of ragged query rows over a paged cache that already holds their own keys.  Query at position
     ``p = ctx_len + t`` sees key ``j`` iff ``j <= p and (p - j < window or j < keep_first)``; ``window <= 0`` means unbounded.
     score = cap * tanh(scale * q.k / cap) (cap <= 0: none), softmax in fp32.  ``gate`` [B, T, Hq * Dv]: the output is multiplied by
-    ``sigmoid(gate)``.  q [B, T, Hq, D] -> [B, T, Hq * Dv]."""
+    ``sigmoid(gate)`` (``gate_per_head``: gate [B, T, Hq], one factor per head).  ``sinks`` [Hq] fp32: ``exp(sinks[h])`` joins the
+    softmax denominator of head ``h`` (a slot without key or value, neither scaled nor capped).  q [B, T, Hq, D] -> [B, T, Hq * Dv]."""
     B, T, Hq, D = q.shape
     page, G, Dv = v_cache.shape[1], v_cache.shape[2], v_cache.shape[3]
     bt = block_table.long().clamp_min(0)
@@ -470,9 +473,15 @@ def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, sca
     if softcap and softcap > 0:
         s = softcap * torch.tanh(s / softcap)
     s = s.masked_fill(~see.unsqueeze(1), float("-inf"))
-    o = torch.einsum("bhts,bshd->bthd", torch.softmax(s, -1), v.repeat_interleave(rep, 2)).reshape(B, T, Hq * Dv)
+    if sinks is not None:
+        s = torch.cat([s, sinks.float().view(1, Hq, 1, 1).expand(B, Hq, T, 1)], -1)
+        pr = torch.softmax(s, -1)[..., :-1]
+    else:
+        pr = torch.softmax(s, -1)
+    o = torch.einsum("bhts,bshd->bthd", pr, v.repeat_interleave(rep, 2)).reshape(B, T, Hq * Dv)
     if gate is not None:
-        o = o * torch.sigmoid(gate.float())
+        gf = torch.sigmoid(gate.float())
+        o = o * (gf.repeat_interleave(Dv, -1) if gate_per_head else gf)
     valid = (torch.arange(T, device=q.device).view(1, T) < q_len.long().view(B, 1)).unsqueeze(-1)
     return torch.where(valid, o, torch.zeros_like(o)).to(q.dtype)
 
@@ -517,3 +526,57 @@ def clamped_glu(gu, limit: float, alpha: float = 1.702):
     g = g.clamp(max=limit)
     u = u.clamp(-limit, limit)
     return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
+
+
+# ---- fp32 residual stream of pre-norm / parallel blocks, latent KV cache, plain experts ---------------------------------------
+def stream_add_rmsnorm(x, adds=(), normed=None, normed_weight=None, vec=None, weight=None, eps: float = 1e-6, lp_dtype=None,
+                       emit_stream_lp: bool = False):
+    """One update of an fp32 residual stream plus the norm that reads it::
+
+        s = [x] + sum(adds) + [rms_unit(normed) * normed_weight] + [vec]            (fp32; every term optional)
+        h = rms_unit(s) * weight                                                   (when ``weight`` is given)
+
+    ``rms_unit(v) = v / sqrt(mean(v^2) + eps)``; ``vec`` is one vector ``[W]`` added to every row.  Returns ``(s fp32, s cast to
+    lp_dtype or None, h in lp_dtype (fp32 when lp_dtype is None) or None)``: the casts feed the next projections."""
+    s = None if x is None else x.float()
+    for y in adds:
+        if y is not None:
+            s = y.float() if s is None else s + y.float()
+    if normed is not None:
+        n = normed.float()
+        n = n * torch.rsqrt(n.pow(2).mean(-1, keepdim=True) + eps)
+        if normed_weight is not None:
+            n = n * normed_weight.float()
+        s = n if s is None else s + n
+    if vec is not None:
+        s = s + vec.float()
+    lp = None if lp_dtype in (None, torch.float32) else lp_dtype
+    h = None
+    if weight is not None:
+        h = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+        h = h if lp is None else h.to(lp)
+    return s, (s.to(lp) if (emit_stream_lp and lp is not None) else None), h
+
+
+def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len):
+    """Channels ``[offset, offset + rank)`` of the projection rows ``p`` [B, T, C] are RMS-normalised (fp32, ``weight`` [rank]) and
+    written to the paged latent cache ``[blocks, page, 1, rank]`` at positions ``ctx_len + t`` for ``t < q_len``."""
+    B, T = p.shape[:2]
+    page = cache.shape[1]
+    c = p[..., offset:offset + rank].float()
+    c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    pos = ctx_len.long().view(B, 1) + torch.arange(T, device=p.device).view(1, T)
+    live = torch.arange(T, device=p.device).view(1, T) < q_len.long().view(B, 1)
+    width = block_table.shape[1]
+    blk = torch.gather(block_table.long(), 1, (pos // page).clamp(0, width - 1))
+    flat = blk * page + pos % page
+    cache.view(-1, rank)[flat[live]] = c[live].to(cache.dtype)
+
+
+def gated_act_mul(gate, other, act: str = "gelu_tanh"):
+    """``act(gate) * other`` in fp32, cast to the type of ``gate``; ``other`` may be a strided slice of a wider row."""
+    return (activation(gate.float(), act) * other.float()).to(gate.dtype)
+
+
+def unary_act(x, act: str):
+    return activation(x.float(), act).to(x.dtype)

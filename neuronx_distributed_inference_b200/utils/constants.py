@@ -99,7 +99,8 @@ MODEL_TYPES.update({"wav2vec2": {"audio-frame-classification":
                                  "neuronx_distributed_inference_b200.contrib.models.wav2vec2:NeuronWav2Vec2ForAudioFrameClassification"}})
 MODEL_TYPES["fetodra"] = {"causal-lm": f"{_P}.fetodra.modeling_fetodra:NeuronFetodraForCausalLM"}
 # checkpoints that name their design by ``architecture`` instead of a Hugging Face ``model_type``
-ARCHITECTURES = {"Fetodra": "fetodra"}
+MODEL_TYPES["sodudra"] = {"causal-lm": f"{_P}.sodudra.modeling_sodudra:NeuronSodudraForCausalLM"}
+ARCHITECTURES = {"Fetodra": "fetodra", "Sodudra": "sodudra"}
 TASK_TYPES = ("causal-lm", "image-text-to-text", "speech-to-text", "text-to-image", "audio-frame-classification", "audio-text-to-text")
 
 
