@@ -113,11 +113,27 @@ __global__ void __launch_bounds__(128) combine_kernel(const T* __restrict__ y, c
   }
 }
 
-// dot product of two dense rows by one warp (every lane gets the sum)
+// dot product of two dense rows by one warp (every lane gets the sum); 16-byte loads when both rows allow them
 template <typename T>
 __device__ __forceinline__ float warp_dot(const T* a, const T* b, int n, int lane) {
+  constexpr int V = 16 / (int)sizeof(T);
   float s = 0.f;
-  for (int c = lane; c < n; c += 32) s = fmaf(ldx(a + c), ldx(b + c), s);
+  if (n % V == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0) {
+    for (int c = lane * V; c < n; c += 32 * V) {
+      const uint4 ua = *reinterpret_cast<const uint4*>(a + c), ub = __ldg(reinterpret_cast<const uint4*>(b + c));
+      if constexpr (V == 4) {
+        s = fmaf(__uint_as_float(ua.x), __uint_as_float(ub.x), s); s = fmaf(__uint_as_float(ua.y), __uint_as_float(ub.y), s);
+        s = fmaf(__uint_as_float(ua.z), __uint_as_float(ub.z), s); s = fmaf(__uint_as_float(ua.w), __uint_as_float(ub.w), s);
+      } else {
+        s = fmaf(bf16lo(ua.x), bf16lo(ub.x), s); s = fmaf(bf16hi(ua.x), bf16hi(ub.x), s);
+        s = fmaf(bf16lo(ua.y), bf16lo(ub.y), s); s = fmaf(bf16hi(ua.y), bf16hi(ub.y), s);
+        s = fmaf(bf16lo(ua.z), bf16lo(ub.z), s); s = fmaf(bf16hi(ua.z), bf16hi(ub.z), s);
+        s = fmaf(bf16lo(ua.w), bf16lo(ub.w), s); s = fmaf(bf16hi(ua.w), bf16hi(ub.w), s);
+      }
+    }
+  } else {
+    for (int c = lane; c < n; c += 32) s = fmaf(ldx(a + c), ldx(b + c), s);
+  }
   return warp_sum(s);
 }
 

@@ -871,6 +871,33 @@ __global__ void __launch_bounds__(256) unary_act_kernel(const T* __restrict__ x,
   if (i < n) stf(out + i, unary_apply(act, ldf(x + i)));
 }
 
+// 16 bytes per thread: `other` rows start at o_stride elements (a multiple of the vector width), C a multiple of it too
+template <typename T, bool MUL>
+__global__ void __launch_bounds__(256) act_vec_kernel(const T* __restrict__ x, const T* __restrict__ other, long long o_stride, T* __restrict__ out,
+                                                      long long nvec, int cvec, int act) {
+  constexpr int V = Vec<T>::N;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const uint4 a = *reinterpret_cast<const uint4*>(x + i * V);
+  uint4 b = make_uint4(0u, 0u, 0u, 0u);
+  if constexpr (MUL) b = *reinterpret_cast<const uint4*>(other + (i / cvec) * o_stride + (i % cvec) * V);
+  uint4 o;
+  if constexpr (V == 4) {
+    float f[4] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w)};
+    const float m[4] = {__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w)};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = unary_apply(act, f[e]) * (MUL ? m[e] : 1.f);
+    o = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  } else {
+    float f[8] = {bf16lo(a.x), bf16hi(a.x), bf16lo(a.y), bf16hi(a.y), bf16lo(a.z), bf16hi(a.z), bf16lo(a.w), bf16hi(a.w)};
+    const float m[8] = {bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y), bf16lo(b.z), bf16hi(b.z), bf16lo(b.w), bf16hi(b.w)};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = unary_apply(act, f[e]) * (MUL ? m[e] : 1.f);
+    o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+  }
+  *reinterpret_cast<uint4*>(out + i * V) = o;
+}
+
 template <typename K>
 void opt_in_smem(K kernel, size_t bytes) {
   if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -916,6 +943,17 @@ void gated_act_mul_launch(const void* gate, const void* other, long long o_strid
                           cudaStream_t st) {
   const long long n = rows * C;
   if (n <= 0) return;
+  const int V = lp ? 8 : 4;
+  if (C % V == 0 && o_stride % V == 0 && (((uintptr_t)gate | (uintptr_t)other | (uintptr_t)out) & 15) == 0) {
+    const long long nvec = n / V;
+    const unsigned gv = (unsigned)((nvec + 255) / 256);
+    if (lp)
+      act_vec_kernel<__nv_bfloat16, true><<<gv, 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)other, o_stride, (__nv_bfloat16*)out, nvec,
+                                                              C / V, act);
+    else
+      act_vec_kernel<float, true><<<gv, 256, 0, st>>>((const float*)gate, (const float*)other, o_stride, (float*)out, nvec, C / V, act);
+    return;
+  }
   const unsigned grid = (unsigned)((n + 255) / 256);
   if (lp)
     gated_act_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)other, o_stride, (__nv_bfloat16*)out,
@@ -926,6 +964,14 @@ void gated_act_mul_launch(const void* gate, const void* other, long long o_strid
 
 void unary_act_launch(const void* x, void* out, long long n, int act, bool lp, cudaStream_t st) {
   if (n <= 0) return;
+  const int V = lp ? 8 : 4;
+  if (n % V == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+    const long long nvec = n / V;
+    const unsigned gv = (unsigned)((nvec + 255) / 256);
+    if (lp) act_vec_kernel<__nv_bfloat16, false><<<gv, 256, 0, st>>>((const __nv_bfloat16*)x, nullptr, 0, (__nv_bfloat16*)out, nvec, 1, act);
+    else act_vec_kernel<float, false><<<gv, 256, 0, st>>>((const float*)x, nullptr, 0, (float*)out, nvec, 1, act);
+    return;
+  }
   const unsigned grid = (unsigned)((n + 255) / 256);
   if (lp) unary_act_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, act);
   else unary_act_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (float*)out, n, act);

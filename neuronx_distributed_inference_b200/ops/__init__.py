@@ -53,9 +53,9 @@ def rmsnorm(x, weight, eps: float, offset: float = 0.0, residual=None):
     if _use_cuda(x) and x.dtype in _FAST_DTYPES and x.shape[-1] % 8 == 0 and weight is not None \
             and weight.dtype == x.dtype:
         stats["rmsnorm"] += 1
-        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()        # (a slice of a wider projection arrives strided)
         if residual is not None:
-            r2 = residual.reshape(-1, x.shape[-1])
+            r2 = residual.reshape(-1, x.shape[-1]).contiguous()
             y, r = _C().rmsnorm(x2, weight, eps, offset, r2)
             return y.view(x.shape), r.view(x.shape)
         y, _ = _C().rmsnorm(x2, weight, eps, offset, None)

@@ -423,7 +423,7 @@ def test_gpu_kernels_match_definitions():
         B, T, H, R, page = 3, 40, 5, 48, 8
         ctx, ql = torch.tensor([0, 13, 30]).int(), torch.tensor([40, 9, 1]).int()
         nblk = 9
-        table = torch.stack([torch.randperm(B * nblk, generator=g)[b * nblk:(b + 1) * nblk] for b in range(B)]).int()
+        table = torch.randperm(B * nblk, generator=g).view(B, nblk).int()          # every row its own pages
         p, lw = rn(B, T, H * 16 + R + H).to(dt), rn(R)
         c1 = rn(B * nblk, page, 1, R).to(dt)
         c2 = c1.clone().to(dev)
@@ -448,7 +448,7 @@ def test_gpu_kernels_match_definitions():
         B, T, H, page = 2, 150, 6, 16
         ctx, ql = torch.tensor([0, 70]).int(), torch.tensor([150, 93]).int()
         nblk = 11
-        table = torch.stack([torch.randperm(B * nblk, generator=g)[b * nblk:(b + 1) * nblk] for b in range(B)]).int()
+        table = torch.randperm(B * nblk, generator=g).view(B, nblk).int()          # every row its own pages
         c, q, gate, sinks = (rn(B * nblk, page, 1, R) * 0.5).bfloat16(), (rn(B, T, H, R) * 0.3).bfloat16(), rn(B, T, H + 3).bfloat16()[..., 3:], rn(H) * 2
         a = ref.paged_window_attention(q.float(), c.float(), c.float(), table, ctx, ql, 0.2, None, None, 0, gate.float(), sinks, True)
         b = ops.paged_window_attention(q.to(dev), c.to(dev), c.to(dev), table.to(dev), ctx.to(dev), ql.to(dev), 0.2, None, None, 0, gate.to(dev),
