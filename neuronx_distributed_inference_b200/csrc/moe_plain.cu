@@ -172,7 +172,95 @@ __global__ void __launch_bounds__(256) decode_down_kernel(const T* __restrict__ 
   if (lane == 0) stx(out + (size_t)tok * H + n, f);
 }
 
+// ---- fp32 router: logits, sigmoid scores, the k largest, renormalised ----------------------------------------------------------------
+// Block = RT tokens whose rows sit in shared memory as fp32; warp w forms the logits of experts w, w + 8, ... for all RT tokens from ONE
+// pass over the expert's weight row, so the router matrix is read once per RT tokens.  Then warp t picks token t's k largest logits
+// (largest first, lowest index on ties; the sigmoid is monotonic, so these are the k largest scores) and divides their scores by
+// their sum + eps when eps >= 0.
+constexpr int RT = 8;
+template <typename T>
+__global__ void __launch_bounds__(256) router_sigmoid_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+                                                                  float* __restrict__ topk_w, int* __restrict__ topk_i, int N, int W, int E, int k,
+                                                                  float renorm_eps) {
+  extern __shared__ float rsm[];               // [RT][W] rows, then [RT][E] logits
+  float* xs = rsm;
+  float* zs = rsm + (size_t)RT * W;
+  const int t0 = blockIdx.x * RT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < RT * W; i += 256) {
+    const int t = i / W, c = i % W;
+    xs[i] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + c) : 0.f;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += 8) {
+    const float* wr = w + (size_t)e * W;
+    float acc[RT];
+#pragma unroll
+    for (int t = 0; t < RT; ++t) acc[t] = 0.f;
+    for (int c = lane; c < W; c += 32) {
+      const float wv = __ldg(wr + c);
+#pragma unroll
+      for (int t = 0; t < RT; ++t) acc[t] = fmaf(xs[t * W + c], wv, acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < RT; ++t) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) zs[t * E + e] = v;
+    }
+  }
+  __syncthreads();
+  const int t = warp;                          // 8 warps, RT = 8 tokens
+  if (t0 + t >= N) return;
+  float* z = zs + t * E;
+  if (logits)
+    for (int e = lane; e < E; e += 32) logits[(size_t)(t0 + t) * E + e] = z[e];
+  float sum = 0.f;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const float sc = 1.f / (1.f + expf(-best));
+    sum += sc;
+    if (lane == 0) {
+      topk_w[(size_t)(t0 + t) * k + j] = sc;
+      topk_i[(size_t)(t0 + t) * k + j] = bi;
+      z[bi] = -INFINITY;                       // taken
+    }
+    __syncwarp();
+  }
+  if (renorm_eps >= 0.f) {
+    const float inv = 1.f / (sum + renorm_eps);
+    for (int j = lane; j < k; j += 32) topk_w[(size_t)(t0 + t) * k + j] *= inv;
+  }
+}
+
 }  // namespace
+
+size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)RT * (size_t)(W + E); }
+
+void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
+                                float renorm_eps, bool lp, cudaStream_t st) {
+  if (N <= 0) return;
+  if (k > E) throw std::runtime_error("router: more experts chosen than there are");
+  const size_t smem = router_smem_bytes(W, E);
+  if (smem > 200 * 1024) throw std::runtime_error("router: row too wide for the shared-memory kernel");
+  const unsigned grid = (unsigned)((N + RT - 1) / RT);
+  if (lp) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(router_sigmoid_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    router_sigmoid_topk_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, w, logits, topk_w, topk_i, N, W, E, k, renorm_eps);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(router_sigmoid_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    router_sigmoid_topk_kernel<float><<<grid, 256, smem, st>>>((const float*)x, w, logits, topk_w, topk_i, N, W, E, k, renorm_eps);
+  }
+}
 
 void moe_plain_gather_launch(const void* x, const int* row_entry, const int* tile_expert, void* xp, int R, int H, int k, bool lp, cudaStream_t st) {
   if (R <= 0) return;

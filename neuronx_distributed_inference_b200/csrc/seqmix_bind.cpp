@@ -365,9 +365,26 @@ at::Tensor moe_plain(const at::Tensor& x, const at::Tensor& w_up, const at::Tens
   return out;
 }
 
+std::tuple<at::Tensor, at::Tensor, at::Tensor> router_sigmoid_topk(const at::Tensor& x, const at::Tensor& w, int64_t k, double renorm_eps) {
+  check_act(x, "router input");
+  check_f32(w, "router weight");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && w.dim() == 2 && w.size(1) == x.size(1) && k >= 1 && k <= w.size(0));
+  const int N = (int)x.size(0), W = (int)x.size(1), E = (int)w.size(0);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto f32 = x.options().dtype(at::kFloat);
+  auto logits = at::empty({N, E}, f32);
+  auto tw = at::empty({N, k}, f32);
+  auto ti = at::empty({N, k}, x.options().dtype(at::kInt));
+  router_sigmoid_topk_launch(x.data_ptr(), w.data_ptr<float>(), logits.data_ptr<float>(), tw.data_ptr<float>(), ti.data_ptr<int>(), N, W, E, (int)k,
+                             (float)renorm_eps, is_lp(x), stream());
+  return {logits, tw, ti};
+}
+
 }  // namespace
 
 void register_seqmix(pybind11::module_& m) {
+  m.def("router_sigmoid_topk", &router_sigmoid_topk);
+  m.def("router_smem_bytes", [](int64_t W, int64_t E) { return (int64_t)router_smem_bytes((int)W, (int)E); });
   m.def("stream_add_rmsnorm", &stream_add_rmsnorm);
   m.def("latent_norm_append", &latent_norm_append);
   m.def("gated_act_mul", &gated_act_mul);

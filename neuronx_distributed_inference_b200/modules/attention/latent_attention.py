@@ -60,9 +60,12 @@ class LatentSinkAttention(nn.Module):
         p = self.in_proj(x)
         cache, _ = kv_mgr.get_kv_by_layer_id(self.layer_idx if cache_index is None else cache_index)
         ops.latent_norm_append(p, self.Cq, R, self.latent_norm_weight, self.eps, cache, meta.block_table, ctx, qlen)
-        a = torch.einsum("bthd,hdr->bthr", p[..., :self.Cq].view(B, T, H, self.head_dim), self.k_up)
+        # batched over heads with strided operands and results: the products land in [B, T, H, .] layout, no transposing copies
+        a = torch.empty(B, T, H, R, dtype=p.dtype, device=p.device)
+        torch.bmm(p.view(B * T, -1)[:, :self.Cq].unflatten(1, (H, self.head_dim)).transpose(0, 1), self.k_up, out=a.view(B * T, H, R).transpose(0, 1))
         gate = p[..., self.Cq + R:] if self.Cg else None
         lat = ops.paged_window_attention(a, cache, cache, meta.block_table, ctx, qlen, self.scale, None, None, 0, gate, self.sinks,
                                          gate_per_head=True)
-        o = torch.einsum("bthr,hvr->bthv", lat.view(B, T, H, R), self.v_up)
-        return self.o_proj(o.reshape(B, T, H * self.v_head_dim))
+        o = torch.empty(B, T, H * self.v_head_dim, dtype=p.dtype, device=p.device)
+        torch.bmm(lat.view(B * T, H, R).transpose(0, 1), self.v_up.transpose(1, 2), out=o.view(B * T, H, self.v_head_dim).transpose(0, 1))
+        return self.o_proj(o)

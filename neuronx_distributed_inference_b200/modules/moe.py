@@ -52,6 +52,8 @@ class RouterTopK(nn.Module):
                                           None if self.linear_router.bias is None else self.linear_router.bias.to(cd)).float()
             w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
             return logits, w, idx
+        if self.linear_router.bias is None:
+            return ops.router_topk(x, self.linear_router.weight, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
         logits = nn.functional.linear(x.float(), self.linear_router.weight, self.linear_router.bias)
         w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
         return logits, w, idx

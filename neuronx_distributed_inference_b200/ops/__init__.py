@@ -349,6 +349,18 @@ def moe_route(router_logits, top_k, act="softmax", normalize=True, act_over_topk
     return ref.moe_route(router_logits, top_k, act, normalize, act_over_topk, renorm_eps)
 
 
+def router_topk(x, weight, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None):
+    """fp32 router: ``logits = x W^T`` (W fp32), then :func:`moe_route`.  Sigmoid routers run as ONE kernel on CUDA (row in shared
+    memory, fp32 products, selection and renormalisation in the same block).  -> (logits, weights [N, k] fp32, expert ids [N, k])."""
+    if (_mix_cuda(x) and act == "sigmoid" and not act_over_topk and weight.dtype == torch.float32 and x.dim() == 2 and top_k <= weight.shape[0]
+            and weight.shape[0] <= 512 and 32 * (x.shape[1] + weight.shape[0]) <= 200 * 1024):
+        stats["router_topk"] += 1
+        return _C().router_sigmoid_topk(x.contiguous(), weight.contiguous(), int(top_k), -1.0 if renorm_eps is None else float(renorm_eps))
+    logits = torch.nn.functional.linear(x.float(), weight.float())
+    w, idx = moe_route(logits, top_k, act, normalize, act_over_topk, renorm_eps)
+    return logits, w, idx
+
+
 def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_offset=0,
                 gate_up_bias=None, down_bias=None, act_fn=None, scale_input=False, gate_up_scale=None, down_scale=None):
     N = x.shape[0]

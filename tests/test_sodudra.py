@@ -372,7 +372,7 @@ def test_gpu_stack_schedules_mixed_batches_and_generation(tmp_path, dtype):
     eng, cfg, w = check_schedules(tmp_path, "cuda", dtype)
     check_mixed_batches(eng, cfg, w, dtype)
     check_generate(eng, cfg, w, dtype)
-    for k in ("stream_add_rmsnorm", "latent_norm_append", "paged_window_attention", "gated_act_mul", "unary_act", "moe_plain"):
+    for k in ("stream_add_rmsnorm", "latent_norm_append", "paged_window_attention", "gated_act_mul", "unary_act", "moe_plain", "router_topk"):
         assert ops.stats[k] > 0, k
     tkg = eng.app.token_generation_model          # single-token steps replayed from CUDA graphs (capture did not fall back to eager)
     assert tkg.use_graphs and len(tkg._graphs) > 0
@@ -444,6 +444,14 @@ def test_gpu_kernels_match_definitions():
             a = ref.moe_experts(xx, wu, wd, tw, ti, "relu2")
             b = ops.moe_experts(xx.to(dev), wu.to(dev), wd.to(dev), tw.to(dev), ti.to(dev), "relu2")
             assert torch.allclose(a.float(), b.float().cpu(), atol=1e-4 if dt == torch.float32 else 6e-2), (N, Hh, I, E, k)
+        for (N, Wd, E, k) in ((37, 72, 6, 3), (1, 200, 33, 33), (300, 256, 64, 1)):        # the router in one kernel: fp32 products, selection, renormalisation
+            xx, wr = rn(N, Wd).to(dt), rn(E, Wd) * Wd ** -0.5
+            lg, tw, ti = ops.router_topk(xx.to(dev), wr.to(dev), k, "sigmoid", True, False, 1e-20)
+            want_lg = xx.double() @ wr.double().T
+            wo, io = oracle.route(want_lg, k)
+            assert torch.allclose(lg.double().cpu(), want_lg, atol=1e-4) and torch.equal(ti.cpu().long(), io)
+            assert torch.allclose(tw.double().cpu(), wo, atol=1e-5)
+            assert ops.stats["router_topk"] > 0
     for R in (128, 64):     # bf16 portions of 16+ tokens with latent rows of 64 / 128 numbers: tensor-core kernel, one kv head for all heads
         B, T, H, page = 2, 150, 6, 16
         ctx, ql = torch.tensor([0, 70]).int(), torch.tensor([150, 93]).int()
