@@ -173,46 +173,77 @@ __global__ void __launch_bounds__(256) decode_down_kernel(const T* __restrict__ 
 }
 
 // ---- fp32 router: logits, sigmoid scores, the k largest, renormalised ----------------------------------------------------------------
-// Block = RT tokens whose rows sit in shared memory as fp32; warp w forms the logits of experts w, w + 8, ... for all RT tokens from ONE
-// pass over the expert's weight row, so the router matrix is read once per RT tokens.  Then warp t picks token t's k largest logits
-// (largest first, lowest index on ties; the sigmoid is monotonic, so these are the k largest scores) and divides their scores by
-// their sum + eps when eps >= 0.
+// Kernel 1 (logits): block = RT tokens whose rows sit in shared memory as fp32 x 8 warps; a warp forms the logits of EG experts for all
+// RT tokens from ONE pass over those experts' weight rows (RT x EG accumulators per lane: EG weight loads and RT shared-memory loads
+// feed RT * EG multiply-adds), so the router matrix is read once per RT tokens.  EG = 4 for prompt portions; EG = 1 for a handful of
+// tokens, where spreading the experts over more blocks matters more than reuse.
+// Kernel 2 (selection): one warp per token picks the k largest logits (largest first, lowest index on ties; the sigmoid is monotonic,
+// so these are the k largest scores), writes their sigmoid scores and divides them by their sum + eps when eps >= 0.
 constexpr int RT = 8;
-template <typename T>
-__global__ void __launch_bounds__(256) router_sigmoid_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
-                                                                  float* __restrict__ topk_w, int* __restrict__ topk_i, int N, int W, int E, int k,
-                                                                  float renorm_eps) {
-  extern __shared__ float rsm[];               // [RT][W] rows, then [RT][E] logits
-  float* xs = rsm;
-  float* zs = rsm + (size_t)RT * W;
+template <typename T, int EG>
+__global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+                                                            int N, int W, int E) {
+  extern __shared__ __align__(16) float rsm[];               // [RT][W]
   const int t0 = blockIdx.x * RT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < RT * W; i += 256) {
     const int t = i / W, c = i % W;
-    xs[i] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + c) : 0.f;
+    rsm[i] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + c) : 0.f;
   }
   __syncthreads();
-  for (int e = warp; e < E; e += 8) {
-    const float* wr = w + (size_t)e * W;
-    float acc[RT];
+  const int e0 = (blockIdx.y * 8 + warp) * EG;
+  if (e0 >= E) return;
+  float acc[RT][EG];
 #pragma unroll
-    for (int t = 0; t < RT; ++t) acc[t] = 0.f;
+  for (int t = 0; t < RT; ++t)
+#pragma unroll
+    for (int g = 0; g < EG; ++g) acc[t][g] = 0.f;
+  const float* wr[EG];
+#pragma unroll
+  for (int g = 0; g < EG; ++g) wr[g] = w + (size_t)min(e0 + g, E - 1) * W;
+  if (W % 4 == 0) {
+    for (int c = lane * 4; c < W; c += 128) {
+      float4 wv[EG];
+#pragma unroll
+      for (int g = 0; g < EG; ++g) wv[g] = __ldg(reinterpret_cast<const float4*>(wr[g] + c));
+#pragma unroll
+      for (int t = 0; t < RT; ++t) {
+        const float4 xv = *reinterpret_cast<const float4*>(rsm + t * W + c);
+#pragma unroll
+        for (int g = 0; g < EG; ++g)
+          acc[t][g] = fmaf(xv.w, wv[g].w, fmaf(xv.z, wv[g].z, fmaf(xv.y, wv[g].y, fmaf(xv.x, wv[g].x, acc[t][g]))));
+      }
+    }
+  } else {
     for (int c = lane; c < W; c += 32) {
-      const float wv = __ldg(wr + c);
+      float wv[EG];
 #pragma unroll
-      for (int t = 0; t < RT; ++t) acc[t] = fmaf(xs[t * W + c], wv, acc[t]);
-    }
+      for (int g = 0; g < EG; ++g) wv[g] = __ldg(wr[g] + c);
 #pragma unroll
-    for (int t = 0; t < RT; ++t) {
-      const float v = warp_sum(acc[t]);
-      if (lane == 0) zs[t * E + e] = v;
+      for (int t = 0; t < RT; ++t) {
+        const float xv = rsm[t * W + c];
+#pragma unroll
+        for (int g = 0; g < EG; ++g) acc[t][g] = fmaf(xv, wv[g], acc[t][g]);
+      }
     }
   }
-  __syncthreads();
-  const int t = warp;                          // 8 warps, RT = 8 tokens
-  if (t0 + t >= N) return;
-  float* z = zs + t * E;
-  if (logits)
-    for (int e = lane; e < E; e += 32) logits[(size_t)(t0 + t) * E + e] = z[e];
+#pragma unroll
+  for (int t = 0; t < RT; ++t)
+#pragma unroll
+    for (int g = 0; g < EG; ++g) {
+      const float v = warp_sum(acc[t][g]);
+      if (lane == 0 && t0 + t < N && e0 + g < E) logits[(size_t)(t0 + t) * E + e0 + g] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, float* __restrict__ topk_w, int* __restrict__ topk_i,
+                                                            int N, int E, int k, float renorm_eps) {
+  extern __shared__ float zsm[];                             // [8][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * 8 + warp;
+  if (tok >= N) return;
+  float* z = zsm + warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)tok * E + e];
+  __syncwarp();
   float sum = 0.f;
   for (int j = 0; j < k; ++j) {
     float best = -INFINITY;
@@ -230,36 +261,41 @@ __global__ void __launch_bounds__(256) router_sigmoid_topk_kernel(const T* __res
     const float sc = 1.f / (1.f + expf(-best));
     sum += sc;
     if (lane == 0) {
-      topk_w[(size_t)(t0 + t) * k + j] = sc;
-      topk_i[(size_t)(t0 + t) * k + j] = bi;
-      z[bi] = -INFINITY;                       // taken
+      topk_w[(size_t)tok * k + j] = sc;
+      topk_i[(size_t)tok * k + j] = bi;
+      z[bi] = -INFINITY;                                     // taken
     }
     __syncwarp();
   }
   if (renorm_eps >= 0.f) {
     const float inv = 1.f / (sum + renorm_eps);
-    for (int j = lane; j < k; j += 32) topk_w[(size_t)(t0 + t) * k + j] *= inv;
+    for (int j = lane; j < k; j += 32) topk_w[(size_t)tok * k + j] *= inv;
   }
 }
 
 }  // namespace
 
-size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)RT * (size_t)(W + E); }
+size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)RT * (size_t)W; }
 
 void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
                                 float renorm_eps, bool lp, cudaStream_t st) {
   if (N <= 0) return;
   if (k > E) throw std::runtime_error("router: more experts chosen than there are");
   const size_t smem = router_smem_bytes(W, E);
-  if (smem > 200 * 1024) throw std::runtime_error("router: row too wide for the shared-memory kernel");
-  const unsigned grid = (unsigned)((N + RT - 1) / RT);
+  if (smem > 200 * 1024 || E > 4096) throw std::runtime_error("router: row too wide for the shared-memory kernel");
+  const bool few = N <= 4 * RT;
+  const int eg = few ? 1 : 4;
+  dim3 grid((N + RT - 1) / RT, (E + 8 * eg - 1) / (8 * eg));
+  auto go = [&](auto kernel, auto xp) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kernel<<<grid, 256, smem, st>>>(xp, w, logits, N, W, E);
+  };
   if (lp) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(router_sigmoid_topk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    router_sigmoid_topk_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, w, logits, topk_w, topk_i, N, W, E, k, renorm_eps);
+    if (few) go(router_logits_kernel<__nv_bfloat16, 1>, (const __nv_bfloat16*)x); else go(router_logits_kernel<__nv_bfloat16, 4>, (const __nv_bfloat16*)x);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(router_sigmoid_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    router_sigmoid_topk_kernel<float><<<grid, 256, smem, st>>>((const float*)x, w, logits, topk_w, topk_i, N, W, E, k, renorm_eps);
+    if (few) go(router_logits_kernel<float, 1>, (const float*)x); else go(router_logits_kernel<float, 4>, (const float*)x);
   }
+  router_select_kernel<<<(N + 7) / 8, 256, sizeof(float) * 8 * (size_t)E, st>>>(logits, topk_w, topk_i, N, E, k, renorm_eps);
 }
 
 void moe_plain_gather_launch(const void* x, const int* row_entry, const int* tile_expert, void* xp, int R, int H, int k, bool lp, cudaStream_t st) {

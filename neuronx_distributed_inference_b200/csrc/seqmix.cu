@@ -826,6 +826,74 @@ __global__ void __launch_bounds__(256) stream_add_rmsnorm_kernel(StreamAddParams
   for (int c = threadIdx.x; c < W; c += blockDim.x) stf(ho + c, so[c] * r * p.w[c]);      // a thread re-reads only what it wrote itself
 }
 
+// The same with four values per thread and access: rows whose width is a multiple of 4 and at most 4 * 256 * NCH; the sums stay in
+// registers between the passes.
+template <typename T> __device__ __forceinline__ float4 ld4(const T* p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  return make_float4(bf16lo(r.x), bf16hi(r.x), bf16lo(r.y), bf16hi(r.y));
+}
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
+template <typename TY, typename TH, int NCH>
+__global__ void __launch_bounds__(256) stream_add_rmsnorm_vec_kernel(StreamAddParams p) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int W = p.W;
+  const float* xr = p.x ? p.x + row * W : nullptr;
+  const TY* y1 = p.y1 ? (const TY*)p.y1 + row * W : nullptr;
+  const TY* y2 = p.y2 ? (const TY*)p.y2 + row * W : nullptr;
+  const TY* yn = p.yn ? (const TY*)p.yn + row * W : nullptr;
+  float4 nv[NCH];
+  float rn = 0.f;
+  if (yn) {
+    float ss = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 256 + threadIdx.x) * 4;
+      nv[ch] = c < W ? ld4(yn + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss += nv[ch].x * nv[ch].x + nv[ch].y * nv[ch].y + nv[ch].z * nv[ch].z + nv[ch].w * nv[ch].w;
+    }
+    rn = 1.f / sqrtf(block_sum(ss, red) / (float)W + p.eps);
+  }
+  float* so = p.s + row * W;
+  __nv_bfloat16* slp = p.s_lp ? (__nv_bfloat16*)p.s_lp + row * W : nullptr;
+  float4 sv[NCH];
+  float ss = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 256 + threadIdx.x) * 4;
+    if (c >= W) { sv[ch] = make_float4(0.f, 0.f, 0.f, 0.f); continue; }
+    float4 s = xr ? ld4(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (y1) { const float4 a = ld4(y1 + c); s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+    if (y2) { const float4 a = ld4(y2 + c); s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+    if (yn) {
+      const float4 g = p.wn ? ld4(p.wn + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+      s.x += nv[ch].x * rn * g.x; s.y += nv[ch].y * rn * g.y; s.z += nv[ch].z * rn * g.z; s.w += nv[ch].w * rn * g.w;
+    }
+    if (p.vec) { const float4 a = ld4(p.vec + c); s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+    st4(so + c, s);
+    if (slp) st4(slp + c, s);
+    ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    sv[ch] = s;
+  }
+  if (!p.h) return;
+  const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + p.eps);
+  TH* ho = (TH*)p.h + row * W;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 256 + threadIdx.x) * 4;
+    if (c >= W) continue;
+    const float4 g = ld4(p.w + c);
+    st4(ho + c, make_float4(sv[ch].x * r * g.x, sv[ch].y * r * g.y, sv[ch].z * r * g.z, sv[ch].w * r * g.w));
+  }
+}
+
 // ---- latent row: RMS norm of a slice of the projection + paged cache write ----------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128) latent_norm_append_kernel(const T* __restrict__ p, long long p_sb, long long p_st, const float* __restrict__ w,
@@ -916,6 +984,24 @@ void scaled_add_rmsnorm_launch(const float* x, const void* y, bool y_lp, const f
 
 void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, cudaStream_t st) {
   if (p.rows <= 0) return;
+  auto al = [](const void* q, size_t a) { return ((uintptr_t)q & (a - 1)) == 0; };
+  const size_t ya = y_lp ? 8 : 16;
+  if (p.W % 4 == 0 && p.W <= 8192 && p.W >= 256 && al(p.x, 16) && al(p.y1, ya) && al(p.y2, ya) && al(p.yn, ya) && al(p.wn, 16) && al(p.vec, 16) &&
+      al(p.w, 16) && al(p.s, 16) && al(p.s_lp, 8) && al(p.h, h_lp ? 8 : 16)) {
+    const int nch = (p.W + 1023) / 1024;
+    auto go = [&](auto k1, auto k2, auto k4, auto k8) {
+      if (nch <= 1) k1<<<p.rows, 256, 0, st>>>(p);
+      else if (nch <= 2) k2<<<p.rows, 256, 0, st>>>(p);
+      else if (nch <= 4) k4<<<p.rows, 256, 0, st>>>(p);
+      else k8<<<p.rows, 256, 0, st>>>(p);
+    };
+#define NXDI_STREAM_VEC(TY, TH) go(stream_add_rmsnorm_vec_kernel<TY, TH, 1>, stream_add_rmsnorm_vec_kernel<TY, TH, 2>, \
+                                   stream_add_rmsnorm_vec_kernel<TY, TH, 4>, stream_add_rmsnorm_vec_kernel<TY, TH, 8>)
+    if (y_lp) { if (h_lp) NXDI_STREAM_VEC(__nv_bfloat16, __nv_bfloat16); else NXDI_STREAM_VEC(__nv_bfloat16, float); }
+    else { if (h_lp) NXDI_STREAM_VEC(float, __nv_bfloat16); else NXDI_STREAM_VEC(float, float); }
+#undef NXDI_STREAM_VEC
+    return;
+  }
   const int threads = p.W >= 1024 ? 256 : 128;
   if (y_lp) {
     if (h_lp) stream_add_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16><<<p.rows, threads, 0, st>>>(p);

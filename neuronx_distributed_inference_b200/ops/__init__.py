@@ -350,10 +350,11 @@ def moe_route(router_logits, top_k, act="softmax", normalize=True, act_over_topk
 
 
 def router_topk(x, weight, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None):
-    """fp32 router: ``logits = x W^T`` (W fp32), then :func:`moe_route`.  Sigmoid routers run as ONE kernel on CUDA (row in shared
-    memory, fp32 products, selection and renormalisation in the same block).  -> (logits, weights [N, k] fp32, expert ids [N, k])."""
+    """fp32 router: ``logits = x W^T`` (W fp32), then :func:`moe_route`.  Sigmoid routers run as two kernels on CUDA (fp32 products
+    with the rows in shared memory; selection and renormalisation, one warp per token) instead of a cast, a library GEMM and six
+    elementwise / sort launches.  -> (logits, weights [N, k] fp32, expert ids [N, k])."""
     if (_mix_cuda(x) and act == "sigmoid" and not act_over_topk and weight.dtype == torch.float32 and x.dim() == 2 and top_k <= weight.shape[0]
-            and weight.shape[0] <= 512 and 32 * (x.shape[1] + weight.shape[0]) <= 200 * 1024):
+            and weight.shape[0] <= 512 and 32 * x.shape[1] <= 200 * 1024):
         stats["router_topk"] += 1
         return _C().router_sigmoid_topk(x.contiguous(), weight.contiguous(), int(top_k), -1.0 if renorm_eps is None else float(renorm_eps))
     logits = torch.nn.functional.linear(x.float(), weight.float())

@@ -204,6 +204,11 @@ def kernel_table(size, batch, prompt, hbm_gbs, tflops):
         x = torch.randn(N, W, device=dev, dtype=bf)
         w_up, w_dn = torch.randn(E, F, W, device=dev, dtype=bf) * W ** -0.5, torch.randn(E, W, F, device=dev, dtype=bf) * F ** -0.5
         w_gu = torch.randn(E, 2 * F, W, device=dev, dtype=bf) * W ** -0.5
+        wr = torch.randn(E, W, device=dev) * W ** -0.5
+        run(f"{phase}: router_topk (fp32 products + selection + renormalisation, two kernels)", lambda: ops.router_topk(x, wr, k, "sigmoid", True, False, 1e-20),
+            N * W * 2 + E * W * 4, 2.0 * N * E * W)
+        run(f"{phase}: like: cast + fp32 library GEMM + sigmoid / top-k / sum / divide (torch)",
+            lambda: ref.moe_route(torch.nn.functional.linear(x.float(), wr), k, "sigmoid", True, False, 1e-20), N * W * 2 + E * W * 4, 2.0 * N * E * W)
         tw, ti = ref.moe_route(torch.randn(N, E, device=dev), k, "sigmoid", True, False, 1e-20)
         ti = ti.to(torch.int32)
         used = min(E, N * k)
