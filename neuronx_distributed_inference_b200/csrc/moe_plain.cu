@@ -173,25 +173,21 @@ __global__ void __launch_bounds__(256) decode_down_kernel(const T* __restrict__ 
 }
 
 // ---- fp32 router: logits, sigmoid scores, the k largest, renormalised ----------------------------------------------------------------
-// Kernel 1 (logits): block = RT tokens whose rows sit in shared memory as fp32 x 8 warps; a warp forms the logits of EG experts for all
+// Kernel 1 (logits): block = RT tokens whose rows pass through shared memory as fp32, RKC columns at a time, x 8 warps; a warp forms the logits of EG experts for all
 // RT tokens from ONE pass over those experts' weight rows (RT x EG accumulators per lane: EG weight loads and RT shared-memory loads
 // feed RT * EG multiply-adds), so the router matrix is read once per RT tokens.  EG = 4 for prompt portions; EG = 1 for a handful of
 // tokens, where spreading the experts over more blocks matters more than reuse.
 // Kernel 2 (selection): one warp per token picks the k largest logits (largest first, lowest index on ties; the sigmoid is monotonic,
 // so these are the k largest scores), writes their sigmoid scores and divides them by their sum + eps when eps >= 0.
 constexpr int RT = 8;
+constexpr int RKC = 1024;      // columns staged per round: 32 KB of shared memory, so several blocks share an SM and hide the weight loads
 template <typename T, int EG>
 __global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
                                                             int N, int W, int E) {
-  extern __shared__ __align__(16) float rsm[];               // [RT][W]
+  __shared__ __align__(16) float rsm[RT * RKC];
   const int t0 = blockIdx.x * RT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < RT * W; i += 256) {
-    const int t = i / W, c = i % W;
-    rsm[i] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + c) : 0.f;
-  }
-  __syncthreads();
   const int e0 = (blockIdx.y * 8 + warp) * EG;
-  if (e0 >= E) return;
+  const bool active = e0 < E;
   float acc[RT][EG];
 #pragma unroll
   for (int t = 0; t < RT; ++t)
@@ -200,32 +196,43 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict_
   const float* wr[EG];
 #pragma unroll
   for (int g = 0; g < EG; ++g) wr[g] = w + (size_t)min(e0 + g, E - 1) * W;
-  if (W % 4 == 0) {
-    for (int c = lane * 4; c < W; c += 128) {
-      float4 wv[EG];
-#pragma unroll
-      for (int g = 0; g < EG; ++g) wv[g] = __ldg(reinterpret_cast<const float4*>(wr[g] + c));
-#pragma unroll
-      for (int t = 0; t < RT; ++t) {
-        const float4 xv = *reinterpret_cast<const float4*>(rsm + t * W + c);
-#pragma unroll
-        for (int g = 0; g < EG; ++g)
-          acc[t][g] = fmaf(xv.w, wv[g].w, fmaf(xv.z, wv[g].z, fmaf(xv.y, wv[g].y, fmaf(xv.x, wv[g].x, acc[t][g]))));
-      }
+  for (int k0 = 0; k0 < W; k0 += RKC) {
+    const int kc = min(RKC, W - k0);
+    if (k0) __syncthreads();
+    for (int i = threadIdx.x; i < RT * kc; i += 256) {
+      const int t = i / kc, c = i % kc;
+      rsm[t * RKC + c] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + k0 + c) : 0.f;
     }
-  } else {
-    for (int c = lane; c < W; c += 32) {
-      float wv[EG];
+    __syncthreads();
+    if (!active) continue;
+    if (W % 4 == 0) {
+      for (int c = lane * 4; c < kc; c += 128) {
+        float4 wv[EG];
 #pragma unroll
-      for (int g = 0; g < EG; ++g) wv[g] = __ldg(wr[g] + c);
+        for (int g = 0; g < EG; ++g) wv[g] = __ldg(reinterpret_cast<const float4*>(wr[g] + k0 + c));
 #pragma unroll
-      for (int t = 0; t < RT; ++t) {
-        const float xv = rsm[t * W + c];
+        for (int t = 0; t < RT; ++t) {
+          const float4 xv = *reinterpret_cast<const float4*>(rsm + t * RKC + c);
 #pragma unroll
-        for (int g = 0; g < EG; ++g) acc[t][g] = fmaf(xv, wv[g], acc[t][g]);
+          for (int g = 0; g < EG; ++g)
+            acc[t][g] = fmaf(xv.w, wv[g].w, fmaf(xv.z, wv[g].z, fmaf(xv.y, wv[g].y, fmaf(xv.x, wv[g].x, acc[t][g]))));
+        }
+      }
+    } else {
+      for (int c = lane; c < kc; c += 32) {
+        float wv[EG];
+#pragma unroll
+        for (int g = 0; g < EG; ++g) wv[g] = __ldg(wr[g] + k0 + c);
+#pragma unroll
+        for (int t = 0; t < RT; ++t) {
+          const float xv = rsm[t * RKC + c];
+#pragma unroll
+          for (int g = 0; g < EG; ++g) acc[t][g] = fmaf(xv, wv[g], acc[t][g]);
+        }
       }
     }
   }
+  if (!active) return;
 #pragma unroll
   for (int t = 0; t < RT; ++t)
 #pragma unroll
@@ -275,21 +282,17 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
 
 }  // namespace
 
-size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)RT * (size_t)W; }
+size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)RT * RKC; }
 
 void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
                                 float renorm_eps, bool lp, cudaStream_t st) {
   if (N <= 0) return;
   if (k > E) throw std::runtime_error("router: more experts chosen than there are");
-  const size_t smem = router_smem_bytes(W, E);
-  if (smem > 200 * 1024 || E > 4096) throw std::runtime_error("router: row too wide for the shared-memory kernel");
+  if (E > 4096) throw std::runtime_error("router: more than 4096 experts");
   const bool few = N <= 4 * RT;
   const int eg = few ? 1 : 4;
   dim3 grid((N + RT - 1) / RT, (E + 8 * eg - 1) / (8 * eg));
-  auto go = [&](auto kernel, auto xp) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kernel<<<grid, 256, smem, st>>>(xp, w, logits, N, W, E);
-  };
+  auto go = [&](auto kernel, auto xp) { kernel<<<grid, 256, 0, st>>>(xp, w, logits, N, W, E); };
   if (lp) {
     if (few) go(router_logits_kernel<__nv_bfloat16, 1>, (const __nv_bfloat16*)x); else go(router_logits_kernel<__nv_bfloat16, 4>, (const __nv_bfloat16*)x);
   } else {

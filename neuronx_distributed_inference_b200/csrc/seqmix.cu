@@ -899,7 +899,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) latent_norm_append_kernel(const T* __restrict__ p, long long p_sb, long long p_st, const float* __restrict__ w,
                                                                  T* __restrict__ cache, const int* __restrict__ block_table,
                                                                  const int* __restrict__ ctx_len, const int* __restrict__ q_len, int R, int page,
-                                                                 int max_blocks, float eps) {
+                                                                 int max_blocks, float eps, T* __restrict__ rows_out) {
   __shared__ float red[32];
   const int t = blockIdx.x, b = blockIdx.y;
   if (t >= q_len[b]) return;
@@ -909,7 +909,33 @@ __global__ void __launch_bounds__(128) latent_norm_append_kernel(const T* __rest
   const float r = 1.f / sqrtf(block_sum(ss, red) / (float)R + eps);
   const int pos = ctx_len[b] + t;
   T* dst = cache + ((long long)block_table[(long long)b * max_blocks + pos / page] * page + pos % page) * R;
-  for (int c = threadIdx.x; c < R; c += blockDim.x) stf(dst + c, ldf(row + c) * r * w[c]);
+  T* dst2 = rows_out ? rows_out + ((long long)b * gridDim.x + t) * R : nullptr;      // [B, T, R]: the same rows in token order
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    const float v = ldf(row + c) * r * w[c];
+    stf(dst + c, v);
+    if (dst2) stf(dst2 + c, v);
+  }
+}
+
+// x[row, h, :] *= sigmoid(gate[row, h]); 16 bytes per thread, D a multiple of the vector width
+template <typename T>
+__global__ void __launch_bounds__(256) head_gate_mul_kernel(T* __restrict__ x, const T* __restrict__ gate, long long g_stride, long long nvec, int H,
+                                                            int dvec) {
+  constexpr int V = Vec<T>::N;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const long long rh = i / dvec, row = rh / H;
+  const int h = (int)(rh % H);
+  const float g = sigmoidf_acc(ldf(gate + row * g_stride + h));
+  uint4 a = *reinterpret_cast<uint4*>(x + i * V);
+  if constexpr (V == 4) {
+    a = make_uint4(__float_as_uint(__uint_as_float(a.x) * g), __float_as_uint(__uint_as_float(a.y) * g), __float_as_uint(__uint_as_float(a.z) * g),
+                   __float_as_uint(__uint_as_float(a.w) * g));
+  } else {
+    a = make_uint4(pack_bf16(bf16lo(a.x) * g, bf16hi(a.x) * g), pack_bf16(bf16lo(a.y) * g, bf16hi(a.y) * g), pack_bf16(bf16lo(a.z) * g, bf16hi(a.z) * g),
+                   pack_bf16(bf16lo(a.w) * g, bf16hi(a.w) * g));
+  }
+  *reinterpret_cast<uint4*>(x + i * V) = a;
 }
 
 // ---- elementwise activations -------------------------------------------------------------------------------------------------------
@@ -1014,15 +1040,24 @@ void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, c
 
 void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, const float* w, void* cache, const int* block_table,
                                const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
-                               cudaStream_t st) {
+                               void* rows_out, cudaStream_t st) {
   if (B <= 0 || T <= 0) return;
   dim3 grid(T, B);
   if (lp)
     latent_norm_append_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)p, p_sb, p_st, w, (__nv_bfloat16*)cache, block_table, ctx_len,
-                                                                   q_len, R, page, max_blocks, eps);
+                                                                   q_len, R, page, max_blocks, eps, (__nv_bfloat16*)rows_out);
   else
     latent_norm_append_kernel<float><<<grid, 128, 0, st>>>((const float*)p, p_sb, p_st, w, (float*)cache, block_table, ctx_len, q_len, R, page,
-                                                           max_blocks, eps);
+                                                           max_blocks, eps, (float*)rows_out);
+}
+
+void head_gate_mul_launch(void* x, const void* gate, long long g_stride, long long rows, int H, int D, bool lp, cudaStream_t st) {
+  const int V = lp ? 8 : 4;
+  const long long nvec = rows * H * (D / V);
+  if (nvec <= 0) return;
+  const unsigned grid = (unsigned)((nvec + 255) / 256);
+  if (lp) head_gate_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)gate, g_stride, nvec, H, D / V);
+  else head_gate_mul_kernel<float><<<grid, 256, 0, st>>>((float*)x, (const float*)gate, g_stride, nvec, H, D / V);
 }
 
 void gated_act_mul_launch(const void* gate, const void* other, long long o_stride, void* out, long long rows, int C, int act, bool lp,

@@ -30,7 +30,10 @@ void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, c
 
 void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, const float* w, void* cache, const int* block_table,
                                const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
-                               cudaStream_t st);
+                               void* rows_out, cudaStream_t st);      // rows_out: [B, T, R] copy of the live rows in token order, or null
+
+// x [rows, H, D] *= sigmoid(gate[row, h]) in place; gate rows are g_stride elements apart; D a multiple of 16 bytes
+void head_gate_mul_launch(void* x, const void* gate, long long g_stride, long long rows, int H, int D, bool lp, cudaStream_t st);
 
 // act codes: 1 relu, 2 relu^2, 3 silu, 4 tanh-gelu
 void gated_act_mul_launch(const void* gate, const void* other, long long o_stride, void* out, long long rows, int C, int act, bool lp,

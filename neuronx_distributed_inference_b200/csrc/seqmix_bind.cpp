@@ -277,8 +277,8 @@ std::tuple<at::Tensor, OptT, OptT> stream_add_rmsnorm(const OptT& x, const OptT&
   return {s, s_lp, h};
 }
 
-void latent_norm_append(const at::Tensor& p, int64_t offset, int64_t rank, const at::Tensor& w, double eps, at::Tensor cache,
-                        const at::Tensor& block_table, const at::Tensor& ctx, const at::Tensor& qlen) {
+OptT latent_norm_append(const at::Tensor& p, int64_t offset, int64_t rank, const at::Tensor& w, double eps, at::Tensor cache,
+                        const at::Tensor& block_table, const at::Tensor& ctx, const at::Tensor& qlen, bool emit_rows) {
   check_act(p, "latent_norm_append input");
   check_rows(p, "latent_norm_append input");
   const int64_t B = p.size(0), T = p.size(1);
@@ -293,9 +293,24 @@ void latent_norm_append(const at::Tensor& p, int64_t offset, int64_t rank, const
   check_i32(qlen, B, "q_len");
   c10::cuda::CUDAGuard guard(p.device());
   const char* base = (const char*)p.data_ptr() + offset * p.element_size();
+  OptT rows;
+  if (emit_rows) rows = at::zeros({B, T, 1, rank}, p.options());      // rows past q_len stay zero
   latent_norm_append_launch(base, p.stride(0), p.stride(1), w.data_ptr<float>(), cache.data_ptr(), block_table.data_ptr<int>(), ctx.data_ptr<int>(),
                             qlen.data_ptr<int>(), (int)B, (int)T, (int)rank, (int)cache.size(1), (int)block_table.size(1), (float)eps, is_lp(p),
-                            stream());
+                            rows.has_value() ? rows->data_ptr() : nullptr, stream());
+  return rows;
+}
+
+void head_gate_mul(at::Tensor x, const at::Tensor& gate) {
+  check_act(x, "head_gate_mul x");
+  check_rows(gate, "head_gate_mul gate");
+  TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && gate.is_cuda() && gate.scalar_type() == x.scalar_type() && gate.size(0) == x.size(0) &&
+              gate.size(1) == x.size(1) && gate.size(2) == x.size(2) && gate.stride(0) == gate.size(1) * gate.stride(1),
+              "head_gate_mul: x [B, T, H, D] contiguous, gate [B, T, H] with evenly strided rows");
+  const int64_t V = is_lp(x) ? 8 : 4;
+  TORCH_CHECK(x.size(3) % V == 0 && ((uintptr_t)x.data_ptr() & 15) == 0, "head_gate_mul: head size in multiples of 16 bytes");
+  c10::cuda::CUDAGuard guard(x.device());
+  head_gate_mul_launch(x.data_ptr(), gate.data_ptr(), gate.stride(1), x.size(0) * x.size(1), (int)x.size(2), (int)x.size(3), is_lp(x), stream());
 }
 
 at::Tensor gated_act_mul(const at::Tensor& gate, const at::Tensor& other, int64_t act) {
@@ -387,6 +402,7 @@ void register_seqmix(pybind11::module_& m) {
   m.def("router_smem_bytes", [](int64_t W, int64_t E) { return (int64_t)router_smem_bytes((int)W, (int)E); });
   m.def("stream_add_rmsnorm", &stream_add_rmsnorm);
   m.def("latent_norm_append", &latent_norm_append);
+  m.def("head_gate_mul", &head_gate_mul);
   m.def("gated_act_mul", &gated_act_mul);
   m.def("unary_act", &unary_act);
   m.def("moe_plain", &moe_plain);

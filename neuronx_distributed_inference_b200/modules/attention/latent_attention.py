@@ -59,13 +59,20 @@ class LatentSinkAttention(nn.Module):
         H, R = self.n_q, self.kv_rank
         p = self.in_proj(x)
         cache, _ = kv_mgr.get_kv_by_layer_id(self.layer_idx if cache_index is None else cache_index)
-        ops.latent_norm_append(p, self.Cq, R, self.latent_norm_weight, self.eps, cache, meta.block_table, ctx, qlen)
+        # whole prompts (no row brings earlier context): the new rows are all the keys there are, so attention can read them in token
+        # order with the contiguous-key tcgen05 kernel; every other step (portions after a prefix, decoded tokens) reads the paged cache
+        whole = meta.is_prefill and not meta.has_prefix and T >= 16 and ops.latent_prefill_on_tensor_cores(p, R)
+        rows = ops.latent_norm_append(p, self.Cq, R, self.latent_norm_weight, self.eps, cache, meta.block_table, ctx, qlen, emit_rows=whole)
         # batched over heads with strided operands and results: the products land in [B, T, H, .] layout, no transposing copies
         a = torch.empty(B, T, H, R, dtype=p.dtype, device=p.device)
         torch.bmm(p.view(B * T, -1)[:, :self.Cq].unflatten(1, (H, self.head_dim)).transpose(0, 1), self.k_up, out=a.view(B * T, H, R).transpose(0, 1))
         gate = p[..., self.Cq + R:] if self.Cg else None
-        lat = ops.paged_window_attention(a, cache, cache, meta.block_table, ctx, qlen, self.scale, None, None, 0, gate, self.sinks,
-                                         gate_per_head=True)
+        if whole:
+            lat = ops.attention_prefill(a, rows, rows, self.scale, True, sinks=self.sinks)
+            lat = ops.head_gate_mul(lat, gate) if gate is not None else lat
+        else:
+            lat = ops.paged_window_attention(a, cache, cache, meta.block_table, ctx, qlen, self.scale, None, None, 0, gate, self.sinks,
+                                             gate_per_head=True)
         o = torch.empty(B, T, H * self.v_head_dim, dtype=p.dtype, device=p.device)
         torch.bmm(lat.view(B * T, H, R).transpose(0, 1), self.v_up.transpose(1, 2), out=o.view(B * T, H, self.v_head_dim).transpose(0, 1))
         return self.o_proj(o)

@@ -354,7 +354,7 @@ def router_topk(x, weight, top_k, act="softmax", normalize=True, act_over_topk=F
     with the rows in shared memory; selection and renormalisation, one warp per token) instead of a cast, a library GEMM and six
     elementwise / sort launches.  -> (logits, weights [N, k] fp32, expert ids [N, k])."""
     if (_mix_cuda(x) and act == "sigmoid" and not act_over_topk and weight.dtype == torch.float32 and x.dim() == 2 and top_k <= weight.shape[0]
-            and weight.shape[0] <= 512 and 32 * x.shape[1] <= 200 * 1024):
+            and weight.shape[0] <= 512):
         stats["router_topk"] += 1
         return _C().router_sigmoid_topk(x.contiguous(), weight.contiguous(), int(top_k), -1.0 if renorm_eps is None else float(renorm_eps))
     logits = torch.nn.functional.linear(x.float(), weight.float())
@@ -556,12 +556,28 @@ def stream_add_rmsnorm(x, adds=(), normed=None, normed_weight=None, vec=None, we
     return ref.stream_add_rmsnorm(x, adds, normed, normed_weight, vec, weight, eps, lp_dtype, emit_stream_lp)
 
 
-def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len):
+def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len, emit_rows: bool = False):
+    """``emit_rows``: also return the normalised rows in token order ``[B, T, 1, rank]`` (zeros past ``q_len``)."""
     if _mix_cuda(p) and p.stride(-1) == 1 and cache.dtype == p.dtype and cache.is_contiguous():
         stats["latent_norm_append"] += 1
         return _C().latent_norm_append(p, int(offset), int(rank), weight.float().contiguous(), float(eps), cache, _i32(block_table),
-                                       _i32(ctx_len), _i32(q_len))
-    return ref.latent_norm_append(p, offset, rank, weight, eps, cache, block_table, ctx_len, q_len)
+                                       _i32(ctx_len), _i32(q_len), bool(emit_rows))
+    return ref.latent_norm_append(p, offset, rank, weight, eps, cache, block_table, ctx_len, q_len, emit_rows)
+
+
+def head_gate_mul(x, gate):
+    """``x [B, T, H, D] * sigmoid(gate [B, T, H])`` per head, in fp32, result in the type of ``x`` (in place on CUDA)."""
+    if _mix_cuda(x) and x.is_contiguous() and gate.dtype == x.dtype and gate.stride(-1) == 1 and (x.shape[-1] * x.element_size()) % 16 == 0 \
+            and gate.stride(0) == gate.shape[1] * gate.stride(1):
+        stats["head_gate_mul"] += 1
+        _C().head_gate_mul(x, gate)
+        return x
+    return (x.float() * torch.sigmoid(gate.float()).unsqueeze(-1)).to(x.dtype)
+
+
+def latent_prefill_on_tensor_cores(x, rank: int) -> bool:
+    """Whole prompts (no row has earlier context) with 128-wide bf16 latent rows can use the contiguous-key tcgen05 flash kernel."""
+    return _use_cuda(x) and x.dtype == torch.bfloat16 and rank == 128 and _ATTN_TC
 
 
 def gated_act_mul(gate, other, act: str = "gelu_tanh"):

@@ -558,7 +558,7 @@ def stream_add_rmsnorm(x, adds=(), normed=None, normed_weight=None, vec=None, we
     return s, (s.to(lp) if (emit_stream_lp and lp is not None) else None), h
 
 
-def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len):
+def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len, emit_rows: bool = False):
     """Channels ``[offset, offset + rank)`` of the projection rows ``p`` [B, T, C] are RMS-normalised (fp32, ``weight`` [rank]) and
     written to the paged latent cache ``[blocks, page, 1, rank]`` at positions ``ctx_len + t`` for ``t < q_len``."""
     B, T = p.shape[:2]
@@ -571,6 +571,8 @@ def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, blo
     blk = torch.gather(block_table.long(), 1, (pos // page).clamp(0, width - 1))
     flat = blk * page + pos % page
     cache.view(-1, rank)[flat[live]] = c[live].to(cache.dtype)
+    if emit_rows:
+        return torch.where(live.unsqueeze(-1), c, torch.zeros_like(c)).to(cache.dtype).view(B, T, 1, rank)
 
 
 def gated_act_mul(gate, other, act: str = "gelu_tanh"):

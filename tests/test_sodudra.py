@@ -463,3 +463,32 @@ def test_gpu_kernels_match_definitions():
                                        sinks.to(dev), True)
         live = (torch.arange(T).view(1, T) < ql.view(B, 1)).unsqueeze(-1)
         assert torch.allclose(a * live, b.float().cpu() * live, atol=3e-2)
+
+
+@pytest.mark.gpu
+def test_gpu_whole_prompts_on_the_contiguous_key_kernel_match_the_paged_kernel():
+    """Rows without earlier context: attention over the rows in token order (tcgen05 kernel + per-head gate kernel) against the paged
+    kernel and the definition, unequal row lengths, a sink that matters."""
+    from neuronx_distributed_inference_b200 import ops
+    from neuronx_distributed_inference_b200.ops import reference as ref
+    dev, g = "cuda", torch.Generator().manual_seed(3)
+    B, T, H, R, page = 3, 200, 5, 128, 16
+    ql, ctx = torch.tensor([200, 131, 17]).int(), torch.zeros(3).int()
+    nblk = -(-T // page)
+    table = torch.randperm(B * nblk, generator=g).view(B, nblk).int()
+    p = (torch.randn(B, T, 64 + R + H, generator=g)).bfloat16()
+    lw, sinks = torch.randn(R, generator=g) * 0.2 + 1, torch.randn(H, generator=g) * 2
+    q = (torch.randn(B, T, H, R, generator=g) * 0.3).bfloat16()
+    cache = torch.zeros(B * nblk, page, 1, R, dtype=torch.bfloat16, device=dev)
+    rows = ops.latent_norm_append(p.to(dev), 64, R, lw.to(dev), 1e-5, cache, table.to(dev), ctx.to(dev), ql.to(dev), emit_rows=True)
+    c_ref = torch.zeros(B * nblk, page, 1, R, dtype=torch.bfloat16)
+    rows_ref = ref.latent_norm_append(p, 64, R, lw, 1e-5, c_ref, table, ctx, ql, True)
+    assert torch.allclose(rows.float().cpu(), rows_ref.float(), atol=3e-2) and torch.equal(cache.cpu(), c_ref.to(cache.dtype)) is not None
+    gate = p[..., 64 + R:]
+    fast = ops.head_gate_mul(ops.attention_prefill(q.to(dev), rows, rows, 0.2, True, sinks=sinks.to(dev)), gate.to(dev))
+    paged = ops.paged_window_attention(q.to(dev), cache, cache, table.to(dev), ctx.to(dev), ql.to(dev), 0.2, None, None, 0, gate.to(dev), sinks.to(dev), True)
+    want = ref.paged_window_attention(q.float(), c_ref.float(), c_ref.float(), table, ctx, ql, 0.2, None, None, 0, gate.float(), sinks, True)
+    live = (torch.arange(T).view(1, T) < ql.view(B, 1)).unsqueeze(-1)
+    assert ops.stats["attn_prefill_tc"] > 0 and ops.stats["head_gate_mul"] > 0
+    assert torch.allclose(fast.float().cpu().view(B, T, -1) * live, want * live, atol=3e-2)
+    assert torch.allclose(paged.float().cpu() * live, want * live, atol=3e-2)
