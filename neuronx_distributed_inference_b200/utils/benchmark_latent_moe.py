@@ -197,6 +197,12 @@ def kernel_table(size, batch, prompt, hbm_gbs, tflops):
         kc, vc = (torch.randn(B * nblk, page, G, R, device=dev, dtype=bf) for _ in range(2))
         run(f"{phase}: like: paged_window_attention (grouped kv heads of the same size, no sink / gate)",
             lambda: ops.paged_window_attention(q, kc, vc, table, ctx, ql, D ** -0.5, None, None, 0), B * keys * G * R * 2 * 2 + N * H * R * 2 * 2, attn_flops)
+        if phase == "prefill" and ops.latent_prefill_on_tensor_cores(q, R):
+            rows_t = torch.randn(B, T, 1, R, device=dev, dtype=bf)
+            run("prefill: whole prompts: attention_prefill over the rows in token order (tcgen05, sink)",
+                lambda: ops.attention_prefill(q, rows_t, rows_t, D ** -0.5, True, sinks=sinks), attn_bytes, attn_flops)
+            o_t = torch.randn(B, T, H, R, device=dev, dtype=bf)
+            run("prefill: whole prompts: head_gate_mul", lambda: ops.head_gate_mul(o_t, gate), N * H * R * 2 * 2)
         if phase == "prefill":
             k2, v2 = torch.randn(B, T, G, R, device=dev, dtype=bf), torch.randn(B, T, G, R, device=dev, dtype=bf)
             run("prefill: like: attention_prefill (Llama path, tcgen05, contiguous keys)", lambda: ops.attention_prefill(q, k2, v2, D ** -0.5, True),
