@@ -173,18 +173,18 @@ __global__ void __launch_bounds__(256) decode_down_kernel(const T* __restrict__ 
 }
 
 // ---- fp32 router: logits, sigmoid scores, the k largest, renormalised ----------------------------------------------------------------
-// Kernel 1 (logits): block = RT tokens whose rows pass through shared memory as fp32, RKC columns at a time, x 8 warps; a warp forms the logits of EG experts for all
-// RT tokens from ONE pass over those experts' weight rows (RT x EG accumulators per lane: EG weight loads and RT shared-memory loads
-// feed RT * EG multiply-adds), so the router matrix is read once per RT tokens.  EG = 4 for prompt portions; EG = 1 for a handful of
-// tokens, where spreading the experts over more blocks matters more than reuse.
+// Kernel 1 (logits): block = RT tokens whose rows pass through shared memory as fp32, RKC columns at a time, x 8 warps; a warp forms the
+// logits of EG experts for all RT tokens from ONE pass over those experts' weight rows (RT x EG accumulators per lane: EG weight loads
+// and RT shared-memory loads feed RT * EG multiply-adds), so the router matrix is read once per RT tokens.  RT = 8 (sixteen tokens per block
+// measured slower: fewer resident blocks); EG = 4 for prompt portions, EG = 1 for a handful of tokens, where spreading the experts over
+// more blocks matters more than reuse.
 // Kernel 2 (selection): one warp per token picks the k largest logits (largest first, lowest index on ties; the sigmoid is monotonic,
 // so these are the k largest scores), writes their sigmoid scores and divides them by their sum + eps when eps >= 0.
-constexpr int RT = 8;
-constexpr int RKC = 1024;      // columns staged per round: 32 KB of shared memory, so several blocks share an SM and hide the weight loads
-template <typename T, int EG>
+constexpr int RKC = 1024;      // columns staged per round (4 KB per token), so several blocks share an SM and hide the weight loads
+template <typename T, int EG, int RT>
 __global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
                                                             int N, int W, int E) {
-  __shared__ __align__(16) float rsm[RT * RKC];
+  extern __shared__ __align__(16) float rsm[];               // [RT][RKC]
   const int t0 = blockIdx.x * RT, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e0 = (blockIdx.y * 8 + warp) * EG;
   const bool active = e0 < E;
@@ -199,9 +199,27 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict_
   for (int k0 = 0; k0 < W; k0 += RKC) {
     const int kc = min(RKC, W - k0);
     if (k0) __syncthreads();
-    for (int i = threadIdx.x; i < RT * kc; i += 256) {
-      const int t = i / kc, c = i % kc;
-      rsm[t * RKC + c] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + k0 + c) : 0.f;
+    if (W % 4 == 0) {                     // one 4-wide access per thread and token: 256 threads x 4 = RKC columns
+      const int c = threadIdx.x * 4;
+#pragma unroll
+      for (int t = 0; t < RT; ++t) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < kc && t0 + t < N) {
+          const T* src = x + (size_t)(t0 + t) * W + k0 + c;
+          if constexpr (std::is_same<T, float>::value) {
+            v = *reinterpret_cast<const float4*>(src);
+          } else {
+            const uint2 r = *reinterpret_cast<const uint2*>(src);
+            v = make_float4(bf16lo(r.x), bf16hi(r.x), bf16lo(r.y), bf16hi(r.y));
+          }
+        }
+        *reinterpret_cast<float4*>(rsm + t * RKC + c) = v;
+      }
+    } else {
+      for (int i = threadIdx.x; i < RT * kc; i += 256) {
+        const int t = i / kc, c = i % kc;
+        rsm[t * RKC + c] = t0 + t < N ? ldx(x + (size_t)(t0 + t) * W + k0 + c) : 0.f;
+      }
     }
     __syncthreads();
     if (!active) continue;
@@ -282,21 +300,25 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
 
 }  // namespace
 
-size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)RT * RKC; }
+size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)16 * RKC; }
 
 void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
                                 float renorm_eps, bool lp, cudaStream_t st) {
   if (N <= 0) return;
   if (k > E) throw std::runtime_error("router: more experts chosen than there are");
   if (E > 4096) throw std::runtime_error("router: more than 4096 experts");
-  const bool few = N <= 4 * RT;
-  const int eg = few ? 1 : 4;
-  dim3 grid((N + RT - 1) / RT, (E + 8 * eg - 1) / (8 * eg));
-  auto go = [&](auto kernel, auto xp) { kernel<<<grid, 256, 0, st>>>(xp, w, logits, N, W, E); };
+  const bool few = N <= 32;
+  const int eg = few ? 1 : 4, rt = 8;
+  dim3 grid((N + rt - 1) / rt, (E + 8 * eg - 1) / (8 * eg));
+  const size_t smem = sizeof(float) * (size_t)rt * RKC;
+  auto go = [&](auto kernel, auto xp) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kernel<<<grid, 256, smem, st>>>(xp, w, logits, N, W, E);
+  };
   if (lp) {
-    if (few) go(router_logits_kernel<__nv_bfloat16, 1>, (const __nv_bfloat16*)x); else go(router_logits_kernel<__nv_bfloat16, 4>, (const __nv_bfloat16*)x);
+    if (few) go(router_logits_kernel<__nv_bfloat16, 1, 8>, (const __nv_bfloat16*)x); else go(router_logits_kernel<__nv_bfloat16, 4, 8>, (const __nv_bfloat16*)x);
   } else {
-    if (few) go(router_logits_kernel<float, 1>, (const float*)x); else go(router_logits_kernel<float, 4>, (const float*)x);
+    if (few) go(router_logits_kernel<float, 1, 8>, (const float*)x); else go(router_logits_kernel<float, 4, 8>, (const float*)x);
   }
   router_select_kernel<<<(N + 7) / 8, 256, sizeof(float) * 8 * (size_t)E, st>>>(logits, topk_w, topk_i, N, E, k, renorm_eps);
 }
