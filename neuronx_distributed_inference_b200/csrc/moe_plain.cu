@@ -300,8 +300,6 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
 
 }  // namespace
 
-size_t router_smem_bytes(int W, int E) { return sizeof(float) * (size_t)16 * RKC; }
-
 void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
                                 float renorm_eps, bool lp, cudaStream_t st) {
   if (N <= 0) return;

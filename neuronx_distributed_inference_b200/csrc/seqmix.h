@@ -49,7 +49,6 @@ void moe_plain_decode_launch(const void* x, const void* w_up, const void* w_down
 
 // fp32 router: logits = x W^T (x bf16 or fp32, W fp32 [E, W]) on CUDA cores with the rows in shared memory, then per token the
 // sigmoid scores of the k largest, divided by their sum + renorm_eps when renorm_eps >= 0.  `logits` [N, E] is written and read.
-size_t router_smem_bytes(int W, int E);
 void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
                                 float renorm_eps, bool lp, cudaStream_t st);
 

@@ -399,7 +399,6 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> router_sigmoid_topk(const at::Ten
 
 void register_seqmix(pybind11::module_& m) {
   m.def("router_sigmoid_topk", &router_sigmoid_topk);
-  m.def("router_smem_bytes", [](int64_t W, int64_t E) { return (int64_t)router_smem_bytes((int)W, (int)E); });
   m.def("stream_add_rmsnorm", &stream_add_rmsnorm);
   m.def("latent_norm_append", &latent_norm_append);
   m.def("head_gate_mul", &head_gate_mul);

@@ -380,14 +380,27 @@ def test_gpu_stack_schedules_mixed_batches_and_generation(tmp_path, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rank", [64, 128, 96])
+@pytest.mark.parametrize("rank", [64, 128, 96, 256, 320])
 def test_gpu_wider_stack(tmp_path, dtype, rank):
-    """Latent rows of 64 / 128 numbers (tensor-core attention on bf16 portions) and of another size; experts in multiples of 64 (grouped
-    tensor-core products) beside a size that is not."""
+    """Latent rows of 64 / 128 numbers (tensor-core attention on bf16 portions), of other sizes the kernels take (96, 256) and of one
+    they leave to the op's definition on the device (320); experts in multiples of 64 (grouped tensor-core products) beside a size that
+    is not."""
     layers = [layer(mixer(heads=6, dim=32, vdim=48, kv_rank=rank, scale=0.15), experts=7, top=2, ff=128, shared=160),
               layer(mixer(heads=4, dim=48, vdim=32, kv_rank=rank, scale=0.1), experts=5, top=4, ff=40, shared=64)]
     eng, cfg, w = check_schedules(tmp_path, "cuda", dtype, layers=layers, T=77, width=384, vocab=301, eps=1e-6, seed=7, loop=(0, 1, 2), side=16)
     check_mixed_batches(eng, cfg, w, dtype, n_req=5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layers,kw", [
+    ([layer(mixer(heads=1, dim=4, vdim=4, kv_rank=4), experts=1, top=1, ff=8, shared=None)], dict(loop=None, side=0, cap=None, scale=1.0)),
+    ([layer(experts=None), layer(experts=6, top=6, ff=8)], dict(loop=(0, 2, 3), side=3)),
+    ([layer(mixer(heads=5, dim=6, vdim=10, kv_rank=14)), layer(experts=7, top=2, ff=12, shared=20)], dict(loop=(1, 2, 4), width=100, vocab=31)),
+])
+def test_gpu_other_sizes_and_layouts(tmp_path, dtype, layers, kw):
+    """Sizes that no vector access or tensor-core tile fits (odd widths, one head, one expert) take the scalar kernels and library products."""
+    check_schedules(tmp_path, "cuda", dtype, layers=layers, T=45, seed=5, **kw)
 
 
 @pytest.mark.gpu
