@@ -102,7 +102,7 @@ TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 
 def close(got, want, dtype):
     """float32: the whole block within a tight relative error.  bfloat16: rounding may flip a router's choice between two experts whose
-    scores nearly tie, which moves single positions by more than rounding does, so positions are judged one by one: the typical
+    scores nearly tie, which moves single positions by more than rounding does, so positions are assessed one by one: the typical
     one within the tolerance, few beyond three times that."""
     if dtype == "float32":
         return rel_err(got, want) < TOL[dtype]
