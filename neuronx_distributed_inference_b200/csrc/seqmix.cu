@@ -895,25 +895,45 @@ __global__ void __launch_bounds__(256) stream_add_rmsnorm_vec_kernel(StreamAddPa
 }
 
 // ---- latent row: RMS norm of a slice of the projection + paged cache write ----------------------------------------------------------
+// one warp per token, eight tokens per block: no block-wide synchronisation, the row stays in registers when it is at most 256 wide
 template <typename T>
-__global__ void __launch_bounds__(128) latent_norm_append_kernel(const T* __restrict__ p, long long p_sb, long long p_st, const float* __restrict__ w,
+__global__ void __launch_bounds__(256) latent_norm_append_kernel(const T* __restrict__ p, long long p_sb, long long p_st, const float* __restrict__ w,
                                                                  T* __restrict__ cache, const int* __restrict__ block_table,
-                                                                 const int* __restrict__ ctx_len, const int* __restrict__ q_len, int R, int page,
-                                                                 int max_blocks, float eps, T* __restrict__ rows_out) {
-  __shared__ float red[32];
-  const int t = blockIdx.x, b = blockIdx.y;
+                                                                 const int* __restrict__ ctx_len, const int* __restrict__ q_len, int B, int Tn, int R,
+                                                                 int page, int max_blocks, float eps, T* __restrict__ rows_out) {
+  const int lane = threadIdx.x & 31;
+  const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= (long long)B * Tn) return;
+  const int b = (int)(tok / Tn), t = (int)(tok % Tn);
   if (t >= q_len[b]) return;
   const T* row = p + (long long)b * p_sb + (long long)t * p_st;
+  constexpr int KEEP = 8;                       // values per lane held in registers (rows up to 256 wide)
+  float v[KEEP];
   float ss = 0.f;
-  for (int c = threadIdx.x; c < R; c += blockDim.x) { const float v = ldf(row + c); ss += v * v; }
-  const float r = 1.f / sqrtf(block_sum(ss, red) / (float)R + eps);
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int c = lane + 32 * i;
+    v[i] = c < R ? ldf(row + c) : 0.f;
+    ss += v[i] * v[i];
+  }
+  for (int c = lane + 32 * KEEP; c < R; c += 32) { const float x = ldf(row + c); ss += x * x; }
+  const float r = 1.f / sqrtf(warp_sum(ss) / (float)R + eps);
   const int pos = ctx_len[b] + t;
   T* dst = cache + ((long long)block_table[(long long)b * max_blocks + pos / page] * page + pos % page) * R;
-  T* dst2 = rows_out ? rows_out + ((long long)b * gridDim.x + t) * R : nullptr;      // [B, T, R]: the same rows in token order
-  for (int c = threadIdx.x; c < R; c += blockDim.x) {
-    const float v = ldf(row + c) * r * w[c];
-    stf(dst + c, v);
-    if (dst2) stf(dst2 + c, v);
+  T* dst2 = rows_out ? rows_out + tok * R : nullptr;      // [B, T, R]: the same rows in token order
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int c = lane + 32 * i;
+    if (c < R) {
+      const float o = v[i] * r * w[c];
+      stf(dst + c, o);
+      if (dst2) stf(dst2 + c, o);
+    }
+  }
+  for (int c = lane + 32 * KEEP; c < R; c += 32) {
+    const float o = ldf(row + c) * r * w[c];
+    stf(dst + c, o);
+    if (dst2) stf(dst2 + c, o);
   }
 }
 
@@ -1042,12 +1062,12 @@ void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, co
                                const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
                                void* rows_out, cudaStream_t st) {
   if (B <= 0 || T <= 0) return;
-  dim3 grid(T, B);
+  const unsigned grid = (unsigned)(((long long)B * T + 7) / 8);
   if (lp)
-    latent_norm_append_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)p, p_sb, p_st, w, (__nv_bfloat16*)cache, block_table, ctx_len,
-                                                                   q_len, R, page, max_blocks, eps, (__nv_bfloat16*)rows_out);
+    latent_norm_append_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)p, p_sb, p_st, w, (__nv_bfloat16*)cache, block_table, ctx_len,
+                                                                   q_len, B, T, R, page, max_blocks, eps, (__nv_bfloat16*)rows_out);
   else
-    latent_norm_append_kernel<float><<<grid, 128, 0, st>>>((const float*)p, p_sb, p_st, w, (float*)cache, block_table, ctx_len, q_len, R, page,
+    latent_norm_append_kernel<float><<<grid, 256, 0, st>>>((const float*)p, p_sb, p_st, w, (float*)cache, block_table, ctx_len, q_len, B, T, R, page,
                                                            max_blocks, eps, (float*)rows_out);
 }
 
